@@ -1,0 +1,448 @@
+#!/usr/bin/env python
+"""Benchmark of the switched quantized-linear path on B200.
+
+Workload (N=1): the Llama-3-8B linear-shape sweep -- (K,N) in {(4096,4096), (4096,1024),
+(4096,14336), (14336,4096)} x M in {1,2,...,8192} -- on seeded synthetic tensors with the
+benchmark's value distributions (X ~ N(0,1) with 1% of channels x20, W ~ N(0,0.02) stored as
+uint4 g128).  A "step" is one pass over all 56 (shape, M) points through ``DynamicLinear.forward``
+with the interval LUT that the on-device profiler built just before (conversion and activation
+quantization included).  ``value`` = total 2*M*K*N of a pass / device time of the pass.
+
+With --gpus N > 1 (under torchrun) the same sweep runs tensor-parallel: k/v and gate/up are
+column-split, the (4096,4096) and down projections are row-split and followed by an NCCL
+all-reduce; total work is fixed ("strong" scaling).
+
+``python bench.py --impl reference`` times the reference's CPU path (the numpy port under
+oracle/, since the reference's torch code cannot travel to the GPU box) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES_KN = [(4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)]       # (K, N)
+M_LIST = [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192]
+METRIC = 'switched-linear TFLOPS over the Llama-3-8B shape x M sweep'
+
+
+def algorithmic_bytes(m, k, n):
+    """Bytes one call must move: uint4 base + one (scale, scaled-zero) pair per group + X + Y."""
+    return k * n // 2 + 2 * 2 * (k // 128) * n + 2 * m * k + 2 * m * n
+
+
+def load_peaks():
+    p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {'hbm_gbs': d['hbm_gbs'], 'bf16_tflops': d['bf16_tflops'],
+                'bf16_tflops_sustained': d.get('bf16_tflops_sustained', d['bf16_tflops']), 'source': 'measured'}
+    return {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0, 'source': 'fallback'}
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+         'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+         'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.rows = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits',
+                                          '-i', str(self.gpu), '-lms', '100'], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(',')])
+
+    def stop(self):
+        if not self.proc:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, col in (('hw_slowdown', 5), ('hw_thermal_slowdown', 6), ('sw_thermal_slowdown', 7),
+                              ('sw_power_cap', 8)):
+                if len(r) > col and r[col].lower().startswith('active'):
+                    reasons.add(name)
+        top = sorted(sm)[len(sm) // 2:] if sm else []       # the upper half = samples under load
+        return {'sm_mhz': statistics.median(top) if top else None, 'sm_max_mhz': max(mx) if mx else None,
+                'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle port on the host cores
+# --------------------------------------------------------------------------------------
+CPU_SAMPLE = [((4096, 4096), 16), ((4096, 4096), 256), ((4096, 1024), 1024)]
+
+
+def cpu_pass(cases):
+    """One pass of the reference's CPU path over the sample: dequantize + matmul for the W4A16
+    points, activation quantization + int8 conversion + integer matmul + rescale for M >= 256
+    (the regime where the shipped LUTs choose W8A8)."""
+    from oracle import kairos_oracle as ko
+    flops = 0
+    t0 = time.perf_counter()
+    for (k, n), m, x, res in cases:
+        if m >= 256:
+            ko.y_w8a8(x, res)
+        else:
+            ko.y_w4a16(x, res)
+        flops += 2 * m * k * n
+    return flops, time.perf_counter() - t0
+
+
+def cpu_cases():
+    from oracle import kairos_oracle as ko
+    cases = []
+    for (k, n), m in CPU_SAMPLE:
+        x, w = ko.make_case(m, k, n, seed=0)
+        cases.append(((k, n), m, x, ko.from_module(w)))
+    return cases
+
+
+def cpu_baseline(repeats=2):
+    cases = cpu_cases()
+    cpu_pass(cases)                       # warm-up (BLAS threads, page faults)
+    best = None
+    for _ in range(repeats):
+        flops, dt = cpu_pass(cases)
+        v = flops / dt / 1e12
+        best = v if best is None else max(best, v)
+    return {'value': best, 'unit': 'TFLOPS', 'cores': os.cpu_count(), 'kind': 'port',
+            'sample': 'oracle/kairos_oracle.py (numpy, BLAS on all host threads) incl. dequant/act-quant on '
+                      + ', '.join(f'M={m} K={k} N={n}' for (k, n), m in CPU_SAMPLE)}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    cases = cpu_cases()
+    for _ in range(min(args.warmup, 1) or 1):
+        cpu_pass(cases)
+    steps = max(1, min(args.steps, 5))
+    t_tot, f_tot = 0.0, 0
+    for _ in range(steps):
+        f, dt = cpu_pass(cases)
+        t_tot += dt
+        f_tot += f
+    v = f_tot / t_tot / 1e12
+    sample = ('numpy port of the reference torch path on the host cores; each step = '
+              + ', '.join(f'M={m} K={k} N={n}' for (k, n), m in CPU_SAMPLE) + ' incl. dequant/act-quant')
+    print(json.dumps({
+        'impl': 'reference', 'metric': METRIC, 'value': v, 'unit': 'TFLOPS', 'n_gpus': args.gpus, 'steps': steps,
+        'warmup': args.warmup, 'ms_per_step': 1e3 * t_tot / steps, 'higher_is_better': True,
+        'scaling': 'strong' if args.gpus > 1 else 'weak', 'vs_baseline': None, 'dtype': 'f16/int8', 'data': 'synthetic',
+        'config': {'workload': 'llama3-8b-linear-sweep (bounded CPU sample)'},
+        'cpu_baseline': {'value': v, 'unit': 'TFLOPS', 'cores': os.cpu_count(), 'kind': 'port', 'sample': sample},
+        'e2e': {'value': v, 'unit': 'TFLOPS', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0}))
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+def build_layers(torch, kb, tp, rank, world, device):
+    """One switched linear per (K,N) of the sweep (per-rank shard under tensor parallelism)."""
+    from kairos_b200.synthetic import make_case
+    layers = []
+    for (k, n) in SHAPES_KN:
+        _, w = make_case(1, k, n, seed=0)
+        w = torch.from_numpy(w)
+        if world > 1:
+            layers.append(tp.shard_linear(w, kind=tp.layer_kind(k, n), rank=rank, world=world, device=device))
+        else:
+            lin = torch.nn.Linear(k, n, bias=False, dtype=torch.float16)
+            lin.weight.data = w
+            layers.append(kb.DynamicLinear.from_module(lin.to(device), device))
+    return layers
+
+
+def make_inputs(torch, device, world, rank, tp):
+    from kairos_b200.synthetic import make_case
+    xs = {}
+    for (k, n) in SHAPES_KN:
+        x, _ = make_case(max(M_LIST), k, 4, seed=1)
+        x = torch.from_numpy(x)
+        if world > 1 and tp.layer_kind(k, n) == 'row':
+            ks = k // world
+            x = x[:, rank * ks:(rank + 1) * ks].contiguous()
+        xs[(k, n)] = x
+    return xs
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    import kairos_b200 as kb
+    from kairos_b200 import runtime
+    from kairos_b200._lib import check, lib
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    device = torch.device('cuda', local)
+    tp = None
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', device_id=device)
+        from kairos_b200 import tp as tp_mod
+        tp = tp_mod
+    peaks = load_peaks()
+
+    layers = build_layers(torch, kb, tp, rank, world, device)
+    xs_host = make_inputs(torch, device, world, rank, tp)
+    xs_dev = {kn: x.to(device) for kn, x in xs_host.items()}
+    xs_pin = {kn: x.pin_memory() for kn, x in xs_host.items()}
+    mods = [l.linear if world > 1 else l for l in layers]
+    shapes = [m.shape for m in mods]                       # per-rank (N, K)
+
+    # the bounded conversion cache: room for the int8 form of every layer of the sweep
+    ctx = runtime.Context(device, cache_bytes=192 << 20)
+    kb.DynamicLinear.context = ctx
+    ctx.reserve(max(M_LIST), max(s[0] for s in shapes), max(s[1] for s in shapes))
+
+    # ---- (e) on-device profiler builds the LUT, conversion cost included --------------
+    prof = kb.Profiler(shapes, m_grid=M_LIST, n=args.prof_iters, warmup=3, cache='cold')
+    t_prof = time.perf_counter()
+    prof.profiling(device=device)
+    t_prof = time.perf_counter() - t_prof
+    if world > 1:
+        # all ranks must run the same kernel at a point only for timing symmetry; results
+        # do not depend on it, so each rank keeps its own LUT (per-rank profile)
+        dist.barrier()
+    kb.DynamicLinear.prof = prof
+
+    def one_pass(host=False):
+        for li, (k, n) in enumerate(SHAPES_KN):
+            layer = layers[li]
+            for m in M_LIST:
+                if host:
+                    x = xs_pin[(k, n)][:m]
+                    if world > 1:
+                        layer.forward_host(x)
+                    else:
+                        mod = mods[li]
+                        if m != mod.pre_m:
+                            mod.pre_m = m
+                            mod.comp_type = prof.get_comp_type(mod.shape, m)
+                        y = y_pin[(k, n)][:m]
+                        check(lib.kairos_switched_linear_host(mod._native(), x.data_ptr(), y.data_ptr(), m,
+                                                              mod.comp_type, runtime.stream_ptr()), 'host forward')
+                else:
+                    x = xs_dev[(k, n)][:m]
+                    layer(x.unsqueeze(0))
+
+    y_pin = {(k, n): torch.empty((max(M_LIST), n), dtype=torch.float16).pin_memory() for (k, n) in SHAPES_KN}
+    total_flops = sum(2 * m * k * n for (k, n) in SHAPES_KN for m in M_LIST)
+
+    def timed(host):
+        for _ in range(max(3, args.warmup)):
+            one_pass(host)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(args.steps):
+            one_pass(host)
+        e.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = s.elapsed_time(e)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / args.steps
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    stats0 = ctx.stats()
+    ms_step = timed(False)
+    stats1 = ctx.stats()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e = timed(True)
+
+    # kernels launched per pass: one GEMV/GEMM per point, +1 activation quantization for W8A8,
+    # +1 conversion per cache miss
+    comp_of = {(s, m): prof.get_comp_type(s, m) for s in shapes for m in M_LIST}
+    launches = 0
+    for cid in comp_of.values():
+        launches += 2 if cid == 2 else 1
+    launches = launches * args.steps + (stats1['misses'] - stats0['misses'])
+
+    # ---- per-point table (L2 flushed before every timed call) and rooflines, rank 0, N=1 only ----
+    points, roof, roof_gemv = [], None, None
+    if world == 1:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+        for li, (k, n) in enumerate(SHAPES_KN):
+            mod = mods[li]
+            for m in M_LIST:
+                x = xs_dev[(k, n)][:m]
+                cid = prof.get_comp_type(mod.shape, m)
+                ts = []
+                for _ in range(5):
+                    flush.zero_()
+                    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s.record()
+                    mod._forward(x, m, cid)
+                    e.record()
+                    torch.cuda.synchronize()
+                    ts.append(s.elapsed_time(e))
+                us = 1e3 * statistics.median(ts)
+                fl = 2 * m * k * n
+                points.append({'K': k, 'N': n, 'M': m, 'kernel': kb.COMP_TYPE_ID[cid], 'us': round(us, 2),
+                               'tflops': round(fl / us / 1e6, 2),
+                               'hbm_frac': round(algorithmic_bytes(m, k, n) / (us * 1e-6) / 1e9 / peaks['hbm_gbs'], 3),
+                               'tensor_frac': round(fl / us / 1e6 / peaks['bf16_tflops'], 3)})
+        roof, roof_gemv = dominant_rooflines(torch, kb, mods, xs_dev, prof, peaks, flush)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    out = {
+        'metric': METRIC, 'value': total_flops / (ms_step * 1e-3) / 1e12, 'unit': 'TFLOPS', 'n_gpus': world,
+        'steps': args.steps, 'warmup': max(3, args.warmup), 'ms_per_step': ms_step, 'higher_is_better': True,
+        'scaling': 'strong' if world > 1 else 'weak', 'vs_baseline': None, 'dtype': 'f16/int8 (per LUT choice)',
+        'data': 'synthetic',
+        'config': {'workload': 'llama3-8b-linear-sweep', 'shapes_KN': SHAPES_KN, 'M': M_LIST,
+                   'parallelism': f'tp{world}' if world > 1 else 'single',
+                   'l2': 'inputs larger than L2: a pass touches >400 MB between two uses of any tensor; '
+                         'the per-point table flushes L2 (256 MB write) before every timed call',
+                   'lut': 'profiled on device before the timed region, conversion + act-quant included',
+                   'cache_bytes': 192 << 20, 'profile_seconds': round(t_prof, 1)},
+        'e2e': {'value': total_flops / (ms_e2e * 1e-3) / 1e12, 'unit': 'TFLOPS',
+                'h2d_bytes_per_step': sum(2 * m * (k // world if tp and tp.layer_kind(k, n) == 'row' else k)
+                                          for (k, n) in SHAPES_KN for m in M_LIST),
+                'd2h_bytes_per_step': sum(2 * m * n for (k, n) in SHAPES_KN for m in M_LIST),
+                'ms_per_step': ms_e2e},
+        'gpu_launches': int(launches),
+        'clocks': clocks,
+        'lut': {str(s): prof.seg_perf_list[i] for i, s in enumerate(shapes)},
+        'peaks': peaks,
+    }
+    if roof:
+        out['roofline'] = roof
+        out['roofline_gemv'] = roof_gemv
+    if world == 1:
+        out['cpu_baseline'] = cpu_baseline()
+        out['points'] = points
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def dominant_rooflines(torch, kb, mods, xs_dev, prof, peaks, flush):
+    """Roofline of the kernel that dominates the pass (the M=8192 GEMM of the gate/up shape, in
+    the precision the LUT chose) and of the decode GEMV at M=1 on the same shape."""
+    from kairos_b200 import ops
+    li = 2
+    k, n = SHAPES_KN[li]
+    mod = mods[li]
+    m = max(M_LIST)
+    x = xs_dev[(k, n)][:m]
+    cid = prof.get_comp_type(mod.shape, m)
+    name = kb.COMP_TYPE_ID[cid]
+
+    def time_call(fn, reps=10):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        return statistics.mean(ts) * 1e-3
+
+    if cid == 2:
+        w8 = mod._trans_weight_to_8()
+        xq = torch.empty((m, k), dtype=torch.int8, device=x.device)
+        sx = torch.empty((m,), dtype=torch.float16, device=x.device)
+        ops.quant_fp16_to_int8(xq, x, sx)
+        y = torch.empty((m, n), dtype=torch.float16, device=x.device)
+        t = time_call(lambda: ops.w8a8_gemm_forward_cuda(xq, w8, mod.scales_1, sx, y))
+        peak, peak_note = 2 * peaks['bf16_tflops'], '2 x measured bf16 burst (int8 is nominally 2x bf16)'
+        kern = 'umma_gemm_kernel<int8, tma, BT=256>'
+    elif cid == 5:
+        w16 = mod._trans_weight_to_16()
+        t = time_call(lambda: ops.f16_gemm(x, w16))
+        peak, peak_note = peaks['bf16_tflops'], 'measured bf16 burst'
+        kern = 'umma_gemm_kernel<f16, tma, BT=256>'
+    elif cid == 3:
+        w8 = mod._trans_weight_to_8()
+        t = time_call(lambda: ops.w8a16_gemm(x, w8, mod.scales_1))
+        peak, peak_note = peaks['bf16_tflops'], 'measured bf16 burst'
+        kern = 'umma_gemm_kernel<f16, w8-expand, BT=256>'
+    else:
+        t = time_call(lambda: ops.gemm_forward_cuda_new(x, mod.qweight, mod.scales, mod.scaled_zeros))
+        peak, peak_note = peaks['bf16_tflops'], 'measured bf16 burst'
+        kern = 'umma_gemm_kernel<f16, w4-expand, BT=256>'
+    ach = 2 * m * k * n / t / 1e12
+    roof = {'bound': 'tensor', 'kernel': kern, 'lut_choice': name, 'point': {'M': m, 'K': k, 'N': n},
+            'achieved': ach, 'peak': peak, 'unit': 'TFLOP/s', 'frac': ach / peak, 'traffic': None,
+            'peak_source': f'{peaks["source"]}: {peak_note}', 'us_per_launch': t * 1e6}
+    x1 = xs_dev[(k, n)][:1]
+    t1 = time_call(lambda: ops.gemv_forward_cuda_new(x1, mod.qweight, mod.scales, mod.scaled_zeros, 1, n, k, 128),
+                   reps=20)
+    ach1 = algorithmic_bytes(1, k, n) / t1 / 1e9
+    roof_gemv = {'bound': 'hbm', 'kernel': 'gemv_kernel<1>', 'point': {'M': 1, 'K': k, 'N': n}, 'achieved': ach1,
+                 'peak': peaks['hbm_gbs'], 'unit': 'GB/s', 'frac': ach1 / peaks['hbm_gbs'], 'traffic': None,
+                 'peak_source': f'{peaks["source"]}: stream copy', 'us_per_launch': t1 * 1e6}
+    return roof, roof_gemv
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='kairos_b200', choices=['kairos_b200', 'reference'])
+    ap.add_argument('--prof-iters', type=int, default=20)
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,170 @@
+/* C ABI of the B200 switched quantized-linear library (libkairos_b200.so).
+ *
+ * Every entry point replaces one native function of xiezx23/Kairos's hot path;
+ * the reference file:line is cited beside each declaration.  Conventions:
+ *   - all tensor pointers are DEVICE pointers owned by the caller, 16-byte aligned,
+ *     dense row-major; the library never frees them;
+ *   - work is enqueued on `stream` and is stream-ordered, no hidden synchronisation;
+ *   - return value 0 = success, negative = KAIROS_ERR_* (nothing throws, nothing
+ *     traps on the device); kairos_status_str() explains a code, and
+ *     kairos_last_error() returns the detail message of the last failure on the
+ *     calling thread;
+ *   - the resident weight format is the reference's: `qweight` int16 [N/4, K]
+ *     (AWQ 4-row interleave, 8 nibbles per 32-bit word), factor tensors fp16
+ *     group-major [G_pad, N] with G_pad = ceil(K/128/8)*8, `scaled_zero = -(scale*zero)`;
+ *   - shape rules: N % 4 == 0, K % 128 == 0, M >= 0 (M == 0 is a no-op).
+ */
+#ifndef KAIROS_B200_H
+#define KAIROS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* kairos_stream_t; /* == cudaStream_t */
+
+enum {
+    KAIROS_OK = 0,
+    KAIROS_ERR_SHAPE = -1,     /* dimension rule violated */
+    KAIROS_ERR_ALIGN = -2,     /* pointer not 16-byte aligned / null */
+    KAIROS_ERR_CUDA = -3,      /* a CUDA runtime/driver call failed */
+    KAIROS_ERR_WORKSPACE = -4, /* caller-provided or reserved workspace too small */
+    KAIROS_ERR_CACHE = -5,     /* conversion cache cannot hold the converted weight */
+    KAIROS_ERR_COMP = -6,      /* unknown / unsupported kernel id */
+    KAIROS_ERR_DEVICE = -7,    /* a kernel reported a bounded wait that ran out */
+    KAIROS_ERR_ARG = -8        /* bad handle or argument */
+};
+
+/* kernel ids: COMP_TYPE_NAME of kairos/dynamic_linear.py:8-9 */
+enum {
+    KAIROS_COMP_W4A16_GEMM = 0,
+    KAIROS_COMP_W4A16_GEMV = 1,
+    KAIROS_COMP_W8A8 = 2,
+    KAIROS_COMP_W8A16_GEMM = 3,
+    KAIROS_COMP_FP16 = 5
+};
+
+int kairos_abi_version(void);
+const char* kairos_status_str(int status);
+const char* kairos_last_error(void);
+/* Status word the kernels raise when one of their bounded waits runs out (current device).
+ * Read it after synchronising; clear != 0 resets it.  KAIROS_OK or KAIROS_ERR_DEVICE. */
+int kairos_device_status(int clear);
+
+/* ---- primitive kernels -------------------------------------------------- */
+
+/* Per-token symmetric int8 activation quantization: amax over K in fp32,
+ * scale = max(amax,1e-7)/127 (IEEE division), Xq = rint(x/scale), sx = fp16(scale).
+ * Replaces quant_fp16_to_int8 (kernels/csrc/kairos_kernel/quant/quant_f16_to_i8.cu:88-103)
+ * with the arithmetic of its torch twin quantize_tensor_int8 (kairos/quantization.py:111-141). */
+int kairos_act_quant_i8(const void* X_f16, void* Xq_i8, void* sx_f16, int M, int K, kairos_stream_t stream);
+
+/* uint4 base -> row-major int8 [N,K]: trunc(fp16(fp16(q*s)+sz)) with the *_to8 factors.
+ * Replaces dequant_interleaved_int4_to_int8
+ * (kernels/csrc/kairos_kernel/dequant_awq_format/dequant_i4_to_i8.cu:151-181). */
+int kairos_w4_to_w8(const void* qweight, const void* scales_to8, const void* scaled_zeros_to8, void* W8, int N,
+                    int K, kairos_stream_t stream);
+
+/* uint4 base -> row-major fp16 [N,K]: fp16(fp16(q*s)+sz).
+ * Replaces dequant_interleaved_int4_to_fp16
+ * (kernels/csrc/kairos_kernel/dequant_awq_format/dequant_i4_to_f16.cu:156-186). */
+int kairos_w4_to_f16(const void* qweight, const void* scales, const void* scaled_zeros, void* W16, int N, int K,
+                     kairos_stream_t stream);
+
+/* AWQ interleaved int16 [N/4,K] -> QServe W4A8 byte layout int8 [N,K/2] (N % 32 == 0, K % 64 == 0).
+ * Replaces trans_layout_c16_to_c8_awq
+ * (kernels/csrc/kairos_kernel/trans_layout/trans_layout_marlin_c16_to_c8.cu:113-204). */
+int kairos_awq_to_qserve(const void* qweight, void* out_i8, int N, int K, kairos_stream_t stream);
+
+/* Y[M,N] = X[M,K] . dequant(W)^T (+bias), CUDA-core weight-streaming kernel, 1 <= M <= 32.
+ * Replaces gemv_forward_cuda_new
+ * (thirdparty/AWQ/kernels/csrc/quantization_new/gemv/gemv_cuda.cu:245-463). */
+int kairos_w4a16_gemv(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
+                      const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, kairos_stream_t stream);
+
+/* Bytes of scratch the tensor-core GEMMs need for (M,N,K): split-K partial tiles and
+ * tile counters.  The first KAIROS_GEMM_COUNTER_BYTES of the workspace must be zero
+ * before the first call; the kernels leave them zero again. */
+#define KAIROS_GEMM_COUNTER_BYTES 16384
+size_t kairos_gemm_workspace_bytes(int M, int N, int K);
+
+/* Y = X . dequant(W)^T (+bias): tcgen05 f16 MMA, uint4 dequantized in shared memory.
+ * Replaces gemm_forward_cuda_new
+ * (thirdparty/AWQ/kernels/csrc/quantization_new/gemm/gemm_cuda.cu:1126-1236). */
+int kairos_w4a16_gemm(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
+                      const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, void* workspace,
+                      size_t workspace_bytes, kairos_stream_t stream);
+
+/* Y = X . (fp16(W8)*s1)^T (+bias): tcgen05 f16 MMA, int8 weight widened in shared memory.
+ * Kernel id 3 of kairos/dynamic_linear.py:8-9 (declared there, no kernel in the reference). */
+int kairos_w8a16_gemm(const void* X_f16, const void* W8, const void* scales_1, const void* bias_f16_or_null,
+                      void* Y_f16, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                      kairos_stream_t stream);
+
+/* Y = half(float(Xq.W8^T) * (s1[n]*sx[m])) (+bias): tcgen05 kind::i8, int32 accumulators in TMEM.
+ * acc_i32_or_null, when given, receives the raw int32 accumulators [M,N].
+ * Replaces w8a8_gemm_forward_cuda (thirdparty/AWQ/kernels/csrc/w8a8/w8a8_gemm_cuda.cu:909-955). */
+int kairos_w8a8_gemm(const void* Xq_i8, const void* W8, const void* scales_1, const void* sx_f16,
+                     const void* bias_f16_or_null, void* Y_f16, void* acc_i32_or_null, int M, int N, int K,
+                     void* workspace, size_t workspace_bytes, kairos_stream_t stream);
+
+/* Y = X . W16^T (+bias), fp32 accumulation.  Replaces the cuBLAS call `input @ tmp_weight.T`
+ * (kairos/dynamic_linear.py:163). */
+int kairos_f16_gemm(const void* X_f16, const void* W16, const void* bias_f16_or_null, void* Y_f16, int M, int N,
+                    int K, void* workspace, size_t workspace_bytes, kairos_stream_t stream);
+
+/* ---- interval LUT: M -> kernel id  (kernels/csrc/kairos_kernel/lut/lut.h:8-43) ---- */
+typedef struct kairos_lut kairos_lut;
+kairos_lut* kairos_lut_create(void);
+void kairos_lut_destroy(kairos_lut* t);
+int kairos_lut_record(kairos_lut* t, int r, int comp_type); /* lut.h:35-38 */
+int kairos_lut_get(kairos_lut* t, int m);                   /* lut.h:22-33; KAIROS_ERR_ARG when empty */
+void kairos_lut_shrink_to_fit(kairos_lut* t);               /* lut.h:40-43 */
+int kairos_lut_size(const kairos_lut* t);
+
+/* ---- context: bounded conversion cache + workspaces (one per device) -------------
+ * The reference converts the whole weight on every call into a fresh torch.empty
+ * (kairos/dynamic_linear.py:145-147,159-161); the context keeps converted weights in
+ * an LRU cache of at most `cache_bytes` (0 = convert into a single reusable slot on
+ * every call, i.e. the reference's behaviour; SIZE_MAX = keep everything, which is
+ * the all-formats-resident SwitchLinear of kairos/switch_linear.py:127-131). */
+typedef struct kairos_ctx kairos_ctx;
+kairos_ctx* kairos_ctx_create(size_t cache_bytes);
+void kairos_ctx_destroy(kairos_ctx* ctx);
+/* Pre-size the activation / split-K workspaces for calls up to (max_M, max_N, max_K);
+ * without it they grow on demand (a growth synchronises the device once). */
+int kairos_ctx_reserve(kairos_ctx* ctx, int max_M, int max_N, int max_K);
+/* cache statistics: hits, misses (= conversions run), evictions, bytes in use */
+int kairos_ctx_stats(const kairos_ctx* ctx, uint64_t* hits, uint64_t* misses, uint64_t* evictions,
+                     uint64_t* bytes_in_use);
+void kairos_ctx_clear_cache(kairos_ctx* ctx);
+
+/* ---- one switched linear layer -------------------------------------------- */
+typedef struct kairos_layer kairos_layer;
+/* Registers the resident tensors of one layer (DynamicLinear.from_module output,
+ * kairos/dynamic_linear.py:85-115).  Pointers must stay valid for the layer's life. */
+kairos_layer* kairos_layer_create(kairos_ctx* ctx, int N, int K, const void* qweight, const void* scales,
+                                  const void* scaled_zeros, const void* scales_to8,
+                                  const void* scaled_zeros_to8, const void* scales_1,
+                                  const void* bias_f16_or_null);
+void kairos_layer_destroy(kairos_layer* layer);
+
+/* DynamicLinear._forward (kairos/dynamic_linear.py:131-172): run kernel `comp_type` on
+ * X[M,K] -> Y[M,N].  Activation quantization runs only for W8A8; weight conversion only
+ * for ids 2, 3, 5 and only on a cache miss. */
+int kairos_switched_linear(kairos_layer* layer, const void* X_f16, void* Y_f16, int M, int comp_type,
+                           kairos_stream_t stream);
+/* Convert ahead of use (e.g. on a side stream, one layer ahead): fills the cache entry the
+ * given kernel id needs and returns; a later kairos_switched_linear on any stream waits for it. */
+int kairos_layer_prefetch(kairos_layer* layer, int comp_type, kairos_stream_t stream);
+/* Same call with HOST buffers: copies X in, runs, copies Y out, all on `stream`. */
+int kairos_switched_linear_host(kairos_layer* layer, const void* X_host, void* Y_host, int M, int comp_type,
+                                kairos_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KAIROS_B200_H */

@@ -1,0 +1,202 @@
+// Shared device helpers for the sm_100a kernels: status codes, bounded mbarrier
+// waits, TMA / tcgen05 PTX wrappers and the uint4 -> fp16 unpack.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/kairos_b200.h"
+
+namespace kairos {
+
+// ---- base-format constants (one resident weight: packed uint4, group 128) ----
+constexpr int kGroup = 128;       // K elements sharing one (scale, scaled_zero)
+constexpr int kInterleave = 4;    // weight rows interleaved into one int16 row
+constexpr int kKStride = 64;      // k extent of one interleave block
+
+inline int padded_groups(int K) { return ((K / kGroup + 7) / 8) * 8; }
+
+#define KAIROS_CUDA_OK(expr)                                   \
+    do {                                                       \
+        cudaError_t _e = (expr);                               \
+        if (_e != cudaSuccess) return kairos::note_cuda_error(_e); \
+    } while (0)
+
+int note_cuda_error(cudaError_t e);   // records the message, returns KAIROS_ERR_CUDA
+int launch_status();                  // cudaGetLastError() -> status
+
+// ---------------------------------------------------------------------------
+// uint4 unpack.  A 32-bit word of the base holds, for fixed (row, a, c), the
+// eight values k = 32a + 8b + 2c + d (b = nibble index within each 16-bit half,
+// d = which half).  unpack8 returns four half2, h[b] = (q[b,d=0], q[b,d=1]),
+// i.e. two CONSECUTIVE k for each b.  All results are exact integers 0..15.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void unpack8(uint32_t w, __half2 (&h)[4]) {
+    // (w & 0x000f000f) | 0x64006400  ==  half2(1024 + q_lo, 1024 + q_hi)
+    uint32_t t0, t1, t2, t3;
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(t0) : "r"(w));
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(t1) : "r"(w));
+    const uint32_t w8 = w >> 8;
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(t2) : "r"(w8));
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(t3) : "r"(w8));
+    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));   // 1024
+    const __half2 k64 = __half2half2(__ushort_as_half(0x5400));     // 64
+    const __half2 k16th = __half2half2(__ushort_as_half(0x2c00));   // 1/16
+    h[0] = __hsub2(*reinterpret_cast<__half2*>(&t0), k1024);
+    // (1024 + 16 q) / 16 - 64 = q, exact in one fma
+    h[1] = __hfma2(*reinterpret_cast<__half2*>(&t1), k16th, __hneg2(k64));
+    h[2] = __hsub2(*reinterpret_cast<__half2*>(&t2), k1024);
+    h[3] = __hfma2(*reinterpret_cast<__half2*>(&t3), k16th, __hneg2(k64));
+}
+
+// fp16(fp16(q*s) + z): two roundings, matching torch's mul_ then add_ on fp16.
+__device__ __forceinline__ __half2 scale_then_shift(__half2 q, __half2 s, __half2 z) {
+    // the _rn forms forbid contraction of the pair into one fma
+    return __hadd2_rn(__hmul2_rn(q, s), z);
+}
+
+// 16-byte chunk (four words c = 0..3) -> 32 consecutive-k fp16 values
+// out[kk/2] for kk = 8b + 2c (+d), already scaled.  `out` is 16 half2 in k order.
+__device__ __forceinline__ void dequant_chunk32(const uint4& raw, __half2 s, __half2 z, __half2 (&out)[16]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        __half2 h[4];
+        unpack8(w[c], h);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) out[4 * b + c] = scale_then_shift(h[b], s, z);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// shared-memory / mbarrier / TMA / tcgen05 wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when the limit ran out or another role of this CTA
+// already gave up (`*abort_flag` != 0); the caller then leaves its loop and goes to
+// the common teardown.  The limit is ~2 s of polling; a healthy pipeline waits
+// microseconds.
+constexpr long long kWaitCycles = 4000000000LL;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// 2-D tiled TMA load, completion signalled on an mbarrier of this CTA.  No multicast.
+__device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+            smem_u32(dst)),
+        "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// All tcgen05.mma issued so far by this thread arrive (once) on `bar` when they retire.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+template <bool kInt8>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                     uint32_t accumulate) {
+    if constexpr (kInt8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+// 32 lanes x 16 consecutive 32-bit columns of TMEM -> 16 registers per thread.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128-byte-swizzled operand tile whose rows are 128 bytes and whose 8-row
+// groups are 1024 bytes apart: 64-bit shared-memory matrix descriptor.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF)      // start address / 16
+           | (1ull << 16)                              // leading byte offset (unused with swizzle)
+           | (64ull << 32)                             // stride byte offset 1024 / 16
+           | (1ull << 46)                              // descriptor version (Blackwell)
+           | (2ull << 61);                             // layout: SWIZZLE_128B
+}
+
+}  // namespace kairos

@@ -1,0 +1,606 @@
+// Prefill-side tensor-core GEMMs (path items a10, a11, a12 and kernel id 3):
+// one persistent, warp-specialised tcgen05 kernel template.
+//
+//   D[n, m] (TMEM, 128 lanes x BT columns) += W_tile[128 n, BK] . X_tile[BT m, BK]^T
+//
+// The WEIGHT rows ride on the UMMA M dimension (always 128) and the TOKENS on the UMMA N
+// dimension (BT = 16..256), so a small batch wastes no tensor-core rows and a CTA at
+// BT = 256 amortises every expanded weight element over 256 tokens.
+//
+//   kind::i8  (W8A8):  Xq, W8 int8 via TMA, int32 accumulators, scale epilogue
+//   kind::f16 (FP16):  X, W16 fp16 via TMA, fp32 accumulators
+//   kind::f16 (W4A16): X via TMA; the packed uint4 tile (4 KB per 128x64 weights) via
+//                      TMA, expanded by 8 producer warps into the 128B-swizzled K-major
+//                      fp16 operand tile in shared memory
+//   kind::f16 (W8A16): same, int8 tile widened to fp16 and multiplied by s1[n]
+//
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (+TMEM owner), 2..5 = epilogue
+// (TMEM -> registers -> global), 6..13 = weight expanders (dequant modes only).
+// The accumulator is double-buffered in TMEM so the epilogue of one tile overlaps the
+// main loop of the next.  Small problems are split along K: each split writes its
+// partial tile to scratch, the last one to arrive (per-tile counters) sums the partials
+// in split order (deterministic; exact for int32) and runs the epilogue.
+//
+// Every mbarrier wait is bounded; on a timeout the CTA raises a status word and drains.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace kairos {
+
+enum : int { kModeTma = 0, kModeW4 = 1, kModeW8 = 2 };
+
+constexpr int kTileN = 128;           // weight rows per tile (UMMA M)
+constexpr int kRowBytes = 128;        // K extent of one pipeline stage, in bytes of the MMA operand
+constexpr int kATileBytes = kTileN * kRowBytes;
+constexpr int kNumExpandWarps = 8;
+constexpr int kSmemBudget = 200 * 1024;
+
+struct GemmParams {
+    int M, N, K;
+    int n_tiles, m_tiles, splits, kb_per_split, kb_total;
+    const __half* scales;        // W4 mode: [G_pad, N]
+    const __half* scaled_zeros;  // W4 mode: [G_pad, N]
+    const __half* s1;            // [N]: W8 mode operand scale / int8 epilogue scale
+    const __half* sx;            // [M]: int8 epilogue scale
+    const __half* bias;          // [N] or null
+    __half* Y;                   // [M, N]
+    int32_t* acc_dbg;            // [M, N] or null (int8 only)
+    uint32_t* partials;          // split-K partial tiles
+    unsigned* counters;          // four per output tile (one per 32-row quarter), zero between calls
+    int* status;                 // raised on a bounded wait that ran out
+};
+
+template <bool kInt8, int kMode, int BT>
+struct GemmCfg {
+    static constexpr int kXTileBytes = BT * kRowBytes;
+    static constexpr int kRawBytes = kMode == kModeW4 ? 32 * 128 : (kMode == kModeW8 ? kTileN * 64 : kATileBytes);
+    static constexpr int kStageBytes = kRawBytes + kXTileBytes;
+    static constexpr int kAStages = kMode == kModeTma ? 0 : (BT == 256 ? 3 : 4);
+    static constexpr int kStagesFit = (kSmemBudget - kAStages * kATileBytes) / kStageBytes;
+    static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
+    static constexpr int kBlockK = kInt8 ? 128 : 64;          // elements of K per stage
+    static constexpr int kThreads = kMode == kModeTma ? 192 : 192 + 32 * kNumExpandWarps;
+    static constexpr int kTmemCols = 2 * BT < 32 ? 32 : 2 * BT;
+    static constexpr int kBarBytes = 8 * (2 * kStages + 2 * (kAStages ? kAStages : 1) + 4) + 64;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kAStages * kATileBytes + kBarBytes + 1024;
+    static_assert(kStages >= 2, "pipeline too shallow");
+    static_assert(kRawBytes % 1024 == 0 && kXTileBytes % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+    // instruction descriptor: D format (bits 4-5), A/B formats (7-9, 10-12), K-major both,
+    // N >> 3 at bit 17, M >> 4 at bit 24
+    static constexpr uint32_t kIdesc = (kInt8 ? (2u << 4) | (1u << 7) | (1u << 10) : (1u << 4)) |
+                                       ((uint32_t)(BT >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+};
+
+// int8 x 4 (one 32-bit word, k order) -> two half2 (exact), times s
+__device__ __forceinline__ void widen_s8x4(uint32_t w, __half2 s, __half2& lo, __half2& hi) {
+    const uint32_t u = w ^ 0x80808080u;                         // x + 128 as unsigned bytes
+    uint32_t p0, p1;
+    asm("prmt.b32 %0, %1, %2, 0x5140;" : "=r"(p0) : "r"(u), "r"(0x64646464u));   // (1024 + u0, 1024 + u1)
+    asm("prmt.b32 %0, %1, %2, 0x5342;" : "=r"(p1) : "r"(u), "r"(0x64646464u));   // (1024 + u2, 1024 + u3)
+    const __half2 k1152 = __half2half2(__ushort_as_half(0x6480));                 // 1152
+    lo = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p0), k1152), s);
+    hi = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p1), k1152), s);
+}
+
+template <bool kInt8, int kMode, int BT>
+__global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
+    umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                     const GemmParams p) {
+    using Cfg = GemmCfg<kInt8, kMode, BT>;
+    constexpr int kStages = Cfg::kStages;
+    constexpr int kAStages = Cfg::kAStages;
+    constexpr bool kExpand = kMode != kModeTma;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* stage_base = smem;
+    uint8_t* a_ring = smem + kStages * Cfg::kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(a_ring + kAStages * kATileBytes);
+    uint64_t* full = bars;
+    uint64_t* empty = full + kStages;
+    uint64_t* a_full = empty + kStages;
+    uint64_t* a_empty = a_full + (kAStages ? kAStages : 1);
+    uint64_t* tmem_full = a_empty + (kAStages ? kAStages : 1);
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kExpand ? 1 + kNumExpandWarps : 1);
+        }
+        for (int s = 0; s < kAStages; ++s) {
+            mbar_init(&a_full[s], kNumExpandWarps);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_units = p.n_tiles * p.m_tiles * p.splits;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+                const int split = unit % p.splits;
+                const int tile = unit / p.splits;
+                const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+                const int kb0 = split * p.kb_per_split;
+                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* st = stage_base + s * Cfg::kStageBytes;
+                    mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+                    if constexpr (kMode == kModeW4)        // qweight [N/4, K] int16, box 64 x 32
+                        tma_load_2d(st, &tmap_w, &full[s], kb * 64, n_tile * (kTileN / kInterleave));
+                    else if constexpr (kMode == kModeW8)   // W8 [N, K] int8, box 64 x 128
+                        tma_load_2d(st, &tmap_w, &full[s], kb * 64, n_tile * kTileN);
+                    else                                   // [N, K], box 128 bytes x 128
+                        tma_load_2d(st, &tmap_w, &full[s], kb * Cfg::kBlockK, n_tile * kTileN);
+                    tma_load_2d(st + Cfg::kRawBytes, &tmap_x, &full[s], kb * Cfg::kBlockK, m_tile * BT);
+                    if (++s == kStages) { s = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            int s = 0, as = 0, it = 0;
+            uint32_t phase = 0, aphase = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++it) {
+                const int split = unit % p.splits;
+                const int kb0 = split * p.kb_per_split;
+                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const int b = it & 1;
+                if (!mbar_wait(&tmem_empty[b], ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * BT);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&full[s], phase, abort_flag)) { ok = false; break; }
+                    if constexpr (kExpand)
+                        if (!mbar_wait(&a_full[as], aphase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    uint8_t* st = stage_base + s * Cfg::kStageBytes;
+                    const uint32_t a_addr = kExpand ? smem_u32(a_ring + as * kATileBytes) : smem_u32(st);
+                    const uint64_t adesc = umma_desc_sw128(a_addr);
+                    const uint64_t bdesc = umma_desc_sw128(smem_u32(st + Cfg::kRawBytes));
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)   // 4 x (K = 32 bytes) per 128-byte row; +2 = 32 bytes >> 4
+                        umma<kInt8>(d_tmem, adesc + 2 * j, bdesc + 2 * j, Cfg::kIdesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);
+                    if constexpr (kExpand) {
+                        umma_commit(&a_empty[as]);
+                        if (++as == kAStages) { as = 0; aphase ^= 1; }
+                    }
+                    if (++s == kStages) { s = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(&tmem_full[b]);
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------ epilogue ----------------------------------
+        const int q = warp & 3;                    // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;
+        int it = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++it) {
+            const int tile = unit / p.splits;
+            const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+            const int n = n_tile * kTileN + row;
+            const bool n_ok = n < p.N;
+            const int b = it & 1;
+            float s1f = 0.f;
+            if constexpr (kInt8) s1f = n_ok ? __half2float(__ldg(p.s1 + n)) : 0.f;
+            const bool has_bias = p.bias != nullptr;
+            const __half bias_n = (has_bias && n_ok) ? __ldg(p.bias + n) : __float2half_rn(0.f);
+
+            auto finalize = [&](uint32_t v, int m) {
+                if (!n_ok || m >= p.M) return;
+                __half y;
+                if constexpr (kInt8) {
+                    // half(float(acc) * (float(s1[n]) * float(sx[m])))
+                    // (thirdparty/AWQ/kernels/csrc/w8a8/w8a8_gemm_cuda.cu:896-901)
+                    const float sc = __fmul_rn(s1f, __half2float(__ldg(p.sx + m)));
+                    y = __float2half_rn(__fmul_rn((float)(int32_t)v, sc));
+                    if (p.acc_dbg) p.acc_dbg[(size_t)m * p.N + n] = (int32_t)v;
+                } else {
+                    y = __float2half_rn(__uint_as_float(v));
+                }
+                if (has_bias) y = __hadd(y, bias_n);
+                p.Y[(size_t)m * p.N + n] = y;
+            };
+
+            if (!mbar_wait(&tmem_full[b], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BT);
+            uint32_t* part = p.partials + ((size_t)unit * BT) * kTileN + row;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BT; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c0, r);
+                tmem_ld_wait();
+                if (p.splits == 1) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) finalize(r[c], m_tile * BT + c0 + c);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) part[(size_t)(c0 + c) * kTileN] = r[c];
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[b]);
+
+            if (p.splits > 1) {
+                // Publish this warp's 32-row slice of the partial tile; the warp of the split that
+                // arrives last (per (tile, quarter) counter) sums the slices in split order.  Each
+                // quarter is independent, so no cross-warp barrier is involved.
+                __threadfence();
+                __syncwarp();
+                unsigned prev = 0;
+                if (lane == 0) prev = atomicAdd(p.counters + 4 * tile + q, 1u);
+                prev = __shfl_sync(0xffffffffu, prev, 0);
+                if (prev == (unsigned)p.splits - 1u) {
+                    __threadfence();
+                    const uint32_t* base = p.partials + ((size_t)tile * p.splits * BT) * kTileN + row;
+#pragma unroll 1
+                    for (int c = 0; c < BT; ++c) {
+                        uint32_t v;
+                        if constexpr (kInt8) {
+                            int32_t acc = 0;
+                            for (int sp = 0; sp < p.splits; ++sp)
+                                acc += (int32_t)__ldcg(base + ((size_t)sp * BT + c) * kTileN);
+                            v = (uint32_t)acc;
+                        } else {
+                            float acc = 0.f;
+                            for (int sp = 0; sp < p.splits; ++sp)
+                                acc += __uint_as_float(__ldcg(base + ((size_t)sp * BT + c) * kTileN));
+                            v = __float_as_uint(acc);
+                        }
+                        finalize(v, m_tile * BT + c);
+                    }
+                    __syncwarp();
+                    if (lane == 0) p.counters[4 * tile + q] = 0u;   // ready for the next call
+                }
+            }
+        }
+    } else if constexpr (kExpand) {
+        // ------------------------------ weight expanders --------------------------
+        const int j = threadIdx.x - 192;            // 0..255
+        int n_local, khalf;
+        if constexpr (kMode == kModeW4) {
+            // 16-byte chunk j of the [32][128 B] packed tile: qweight row j/8, weight row
+            // 4*(j/8) + (j%8)/2, k half j%2 (32 consecutive k)
+            n_local = 4 * (j >> 3) + ((j & 7) >> 1);
+            khalf = j & 1;
+        } else {
+            n_local = j >> 1;                       // [128][64 B] int8 tile: row j/2, 32 bytes each
+            khalf = j & 1;
+        }
+        const int swz = n_local & 7;
+        const uint32_t dst_row = (uint32_t)((n_local >> 3) * 1024 + swz * 128);
+        int s = 0, as = 0;
+        uint32_t phase = 0, aphase = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+            const int split = unit % p.splits;
+            const int tile = unit / p.splits;
+            const int n_tile = tile / p.m_tiles;
+            const int kb0 = split * p.kb_per_split;
+            const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+            const int n = n_tile * kTileN + n_local;
+            const bool n_ok = n < p.N;
+            const __half hzero = __float2half_rn(0.f);
+            __half sc_cur = hzero, zc_cur = hzero, sc_nxt = hzero, zc_nxt = hzero;
+            int g_cur = -1;
+            if constexpr (kMode == kModeW8) sc_cur = n_ok ? __ldg(p.s1 + n) : hzero;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if constexpr (kMode == kModeW4) {
+                    const int g = kb >> 1;          // 64-wide k blocks, groups of 128
+                    if (g != g_cur) {
+                        if (g_cur < 0) {
+                            sc_cur = n_ok ? __ldg(p.scales + (size_t)g * p.N + n) : hzero;
+                            zc_cur = n_ok ? __ldg(p.scaled_zeros + (size_t)g * p.N + n) : hzero;
+                        } else {
+                            sc_cur = sc_nxt;
+                            zc_cur = zc_nxt;
+                        }
+                        g_cur = g;
+                        const bool more = n_ok && (2 * (g + 1) < kb1);
+                        sc_nxt = more ? __ldg(p.scales + (size_t)(g + 1) * p.N + n) : hzero;
+                        zc_nxt = more ? __ldg(p.scaled_zeros + (size_t)(g + 1) * p.N + n) : hzero;
+                    }
+                }
+                if (!mbar_wait(&full[s], phase, abort_flag)) { ok = false; break; }
+                const uint8_t* st = stage_base + s * Cfg::kStageBytes;
+                uint4 raw0, raw1;
+                if constexpr (kMode == kModeW4) {
+                    raw0 = *reinterpret_cast<const uint4*>(st + 16 * j);
+                } else {
+                    raw0 = *reinterpret_cast<const uint4*>(st + 32 * j);
+                    raw1 = *reinterpret_cast<const uint4*>(st + 32 * j + 16);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);           // packed tile is in registers
+                if (++s == kStages) { s = 0; phase ^= 1; }
+
+                __half2 w[16];
+                if constexpr (kMode == kModeW4) {
+                    dequant_chunk32(raw0, __half2half2(sc_cur), __half2half2(zc_cur), w);
+                } else {
+                    const __half2 s2 = __half2half2(sc_cur);
+                    widen_s8x4(raw0.x, s2, w[0], w[1]);
+                    widen_s8x4(raw0.y, s2, w[2], w[3]);
+                    widen_s8x4(raw0.z, s2, w[4], w[5]);
+                    widen_s8x4(raw0.w, s2, w[6], w[7]);
+                    widen_s8x4(raw1.x, s2, w[8], w[9]);
+                    widen_s8x4(raw1.y, s2, w[10], w[11]);
+                    widen_s8x4(raw1.z, s2, w[12], w[13]);
+                    widen_s8x4(raw1.w, s2, w[14], w[15]);
+                }
+                if (!mbar_wait(&a_empty[as], aphase ^ 1, abort_flag)) { ok = false; break; }
+                uint8_t* dst = a_ring + as * kATileBytes + dst_row;
+                const uint32_t* u = reinterpret_cast<const uint32_t*>(w);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int chunk = (4 * khalf + i) ^ swz;    // 128-byte swizzle: 16-byte chunk ^ (row % 8)
+                    *reinterpret_cast<uint4*>(dst + 16 * chunk) =
+                        make_uint4(u[4 * i], u[4 * i + 1], u[4 * i + 2], u[4 * i + 3]);
+                }
+                fence_proxy_async_smem();                        // generic-proxy writes -> visible to the MMA
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[as]);
+                if (++as == kAStages) { as = 0; aphase ^= 1; }
+            }
+        }
+    }
+
+    // ------------------------------ teardown --------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, KAIROS_ERR_DEVICE);
+        // let copies that were already issued land before the CTA's shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `elem_bytes` elements; box = box_cols x box_rows.
+static int make_tmap(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
+                     uint64_t cols, uint32_t box_cols, uint32_t box_rows, bool swizzle128) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return note_cuda_error(cudaErrorNotSupported);
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return note_cuda_error(cudaErrorInvalidValue);
+    return KAIROS_OK;
+}
+
+int device_sm_count() {
+    static int sms[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!sms[dev]) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        sms[dev] = v;
+    }
+    return sms[dev];
+}
+
+int* device_status_word();   // api.cu: host-mapped word the kernels raise on a timed-out wait
+
+static int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+struct Plan {
+    int bt, n_tiles, m_tiles, splits, kb_per_split, kb_total;
+    size_t partial_bytes;
+};
+
+static Plan make_plan(int M, int N, int K, bool int8) {
+    Plan pl;
+    pl.bt = token_tile(M);
+    pl.n_tiles = (N + kTileN - 1) / kTileN;
+    pl.m_tiles = (M + pl.bt - 1) / pl.bt;
+    pl.kb_total = K / (int8 ? 128 : 64);
+    const int tiles = pl.n_tiles * pl.m_tiles;
+    const int sms = device_sm_count();
+    int splits = 1;
+    if (tiles < sms) {
+        splits = sms / tiles;
+        const int max_by_k = pl.kb_total / 4 > 0 ? pl.kb_total / 4 : 1;   // at least 4 stages of work per split
+        if (splits > max_by_k) splits = max_by_k;
+        if (splits < 1) splits = 1;
+    }
+    pl.kb_per_split = (pl.kb_total + splits - 1) / splits;
+    pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;
+    pl.partial_bytes = pl.splits > 1 ? (size_t)tiles * pl.splits * pl.bt * kTileN * 4 : 0;
+    return pl;
+}
+
+size_t gemm_workspace_bytes(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return KAIROS_GEMM_COUNTER_BYTES;
+    const Plan a = make_plan(M, N, K, false), b = make_plan(M, N, K, true);
+    return KAIROS_GEMM_COUNTER_BYTES + (a.partial_bytes > b.partial_bytes ? a.partial_bytes : b.partial_bytes);
+}
+
+struct GemmArgs {
+    const void* X;       // [M,K] fp16 or int8
+    const void* W;       // mode-dependent weight operand
+    const __half *scales, *scaled_zeros, *s1, *sx, *bias;
+    void* Y;
+    void* acc_dbg;
+    int M, N, K;
+    void* workspace;
+    size_t workspace_bytes;
+    cudaStream_t stream;
+};
+
+template <bool kInt8, int kMode, int BT>
+static int launch_one(const GemmArgs& a, const Plan& pl) {
+    using Cfg = GemmCfg<kInt8, kMode, BT>;
+    CUtensorMap tw, tx;
+    int rc;
+    if constexpr (kMode == kModeW4)
+        rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)a.N / kInterleave, (uint64_t)a.K, 64, 32,
+                       false);
+    else if constexpr (kMode == kModeW8)
+        rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.N, (uint64_t)a.K, 64, kTileN, false);
+    else if constexpr (kInt8)
+        rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.N, (uint64_t)a.K, 128, kTileN, true);
+    else
+        rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.N, (uint64_t)a.K, 64, kTileN, true);
+    if (rc != KAIROS_OK) return rc;
+    if constexpr (kInt8)
+        rc = make_tmap(&tx, a.X, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.M, (uint64_t)a.K, 128, BT, true);
+    else
+        rc = make_tmap(&tx, a.X, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.M, (uint64_t)a.K, 64, BT, true);
+    if (rc != KAIROS_OK) return rc;
+
+    GemmParams p;
+    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.n_tiles = pl.n_tiles; p.m_tiles = pl.m_tiles; p.splits = pl.splits;
+    p.kb_per_split = pl.kb_per_split; p.kb_total = pl.kb_total;
+    p.scales = a.scales; p.scaled_zeros = a.scaled_zeros; p.s1 = a.s1; p.sx = a.sx; p.bias = a.bias;
+    p.Y = static_cast<__half*>(a.Y);
+    p.acc_dbg = static_cast<int32_t*>(a.acc_dbg);
+    p.counters = static_cast<unsigned*>(a.workspace);
+    p.partials = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(a.workspace) + KAIROS_GEMM_COUNTER_BYTES);
+    p.status = device_status_word();
+    if (!p.status) return KAIROS_ERR_CUDA;
+
+    static bool attr_set = false;    // per instantiation
+    if (!attr_set) {
+        KAIROS_CUDA_OK(cudaFuncSetAttribute(umma_gemm_kernel<kInt8, kMode, BT>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_set = true;
+    }
+    const int units = pl.n_tiles * pl.m_tiles * pl.splits;
+    const int sms = device_sm_count();
+    const int grid = units < sms ? units : sms;
+    umma_gemm_kernel<kInt8, kMode, BT><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(tw, tx, p);
+    return launch_status();
+}
+
+template <bool kInt8, int kMode>
+int launch_gemm(const GemmArgs& a) {
+    if (a.M < 0 || a.N <= 0 || a.K <= 0 || (a.K % kGroup) != 0 || (a.N % kInterleave) != 0) return KAIROS_ERR_SHAPE;
+    if (a.M == 0) return KAIROS_OK;
+    if (!a.X || !a.W || !a.Y || ((uintptr_t)a.X & 15) || ((uintptr_t)a.W & 15) || ((uintptr_t)a.Y & 1))
+        return KAIROS_ERR_ALIGN;
+    const Plan pl = make_plan(a.M, a.N, a.K, kInt8);
+    if (4 * pl.n_tiles * pl.m_tiles > (int)(KAIROS_GEMM_COUNTER_BYTES / sizeof(unsigned)) && pl.splits > 1)
+        return KAIROS_ERR_WORKSPACE;
+    if (!a.workspace || ((uintptr_t)a.workspace & 15) ||
+        a.workspace_bytes < KAIROS_GEMM_COUNTER_BYTES + pl.partial_bytes)
+        return KAIROS_ERR_WORKSPACE;
+    switch (pl.bt) {
+        case 16: return launch_one<kInt8, kMode, 16>(a, pl);
+        case 32: return launch_one<kInt8, kMode, 32>(a, pl);
+        case 64: return launch_one<kInt8, kMode, 64>(a, pl);
+        case 128: return launch_one<kInt8, kMode, 128>(a, pl);
+        default: return launch_one<kInt8, kMode, 256>(a, pl);
+    }
+}
+
+template int launch_gemm<true, kModeTma>(const GemmArgs&);
+template int launch_gemm<false, kModeTma>(const GemmArgs&);
+template int launch_gemm<false, kModeW4>(const GemmArgs&);
+template int launch_gemm<false, kModeW8>(const GemmArgs&);
+
+}  // namespace kairos
+
+using kairos::GemmArgs;
+
+extern "C" size_t kairos_gemm_workspace_bytes(int M, int N, int K) { return kairos::gemm_workspace_bytes(M, N, K); }
+
+extern "C" int kairos_w4a16_gemm(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
+                                 const void* bias, void* Y, int M, int N, int K, void* workspace,
+                                 size_t workspace_bytes, kairos_stream_t stream) {
+    if (!scales || !scaled_zeros) return KAIROS_ERR_ALIGN;
+    GemmArgs a{X, qweight, static_cast<const __half*>(scales), static_cast<const __half*>(scaled_zeros), nullptr,
+               nullptr, static_cast<const __half*>(bias), Y, nullptr, M, N, K, workspace, workspace_bytes,
+               reinterpret_cast<cudaStream_t>(stream)};
+    return kairos::launch_gemm<false, kairos::kModeW4>(a);
+}
+
+extern "C" int kairos_w8a16_gemm(const void* X, const void* W8, const void* scales_1, const void* bias, void* Y, int M,
+                                 int N, int K, void* workspace, size_t workspace_bytes, kairos_stream_t stream) {
+    if (!scales_1) return KAIROS_ERR_ALIGN;
+    GemmArgs a{X, W8, nullptr, nullptr, static_cast<const __half*>(scales_1), nullptr,
+               static_cast<const __half*>(bias), Y, nullptr, M, N, K, workspace, workspace_bytes,
+               reinterpret_cast<cudaStream_t>(stream)};
+    return kairos::launch_gemm<false, kairos::kModeW8>(a);
+}
+
+extern "C" int kairos_w8a8_gemm(const void* Xq, const void* W8, const void* scales_1, const void* sx, const void* bias,
+                                void* Y, void* acc_i32, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                                kairos_stream_t stream) {
+    if (!scales_1 || !sx) return KAIROS_ERR_ALIGN;
+    GemmArgs a{Xq, W8, nullptr, nullptr, static_cast<const __half*>(scales_1), static_cast<const __half*>(sx),
+               static_cast<const __half*>(bias), Y, acc_i32, M, N, K, workspace, workspace_bytes,
+               reinterpret_cast<cudaStream_t>(stream)};
+    return kairos::launch_gemm<true, kairos::kModeTma>(a);
+}
+
+extern "C" int kairos_f16_gemm(const void* X, const void* W16, const void* bias, void* Y, int M, int N, int K,
+                               void* workspace, size_t workspace_bytes, kairos_stream_t stream) {
+    GemmArgs a{X, W16, nullptr, nullptr, nullptr, nullptr, static_cast<const __half*>(bias), Y, nullptr, M, N, K,
+               workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream)};
+    return kairos::launch_gemm<false, kairos::kModeTma>(a);
+}

@@ -1,0 +1,128 @@
+"""The native-operator surface of the reference, re-implemented on the B200 C ABI.
+
+Function names and argument order follow the two extension modules the reference's
+``DynamicLinear`` calls -- ``kairos_cuda_accel`` (kernels/csrc/pybind.cpp:16-24) and
+``awq_backend`` (thirdparty/AWQ/kernels/csrc/pybind.cpp:17-26) -- so a call site can switch
+by changing the import.  All tensors must be contiguous CUDA tensors; work is enqueued on
+torch's current stream (the reference's GEMV/GEMM launch on the legacy default stream).
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import check, lib
+from .runtime import gemm_workspace, stream_ptr
+
+
+def _chk(t, dtype, name):
+    if not (t.is_cuda and t.is_contiguous() and t.dtype == dtype):
+        raise ValueError(f'{name}: expected a contiguous CUDA tensor of {dtype}, got {t.dtype} on {t.device}')
+    return t.data_ptr()
+
+
+# ---- kairos_cuda_accel ------------------------------------------------------
+def quant_fp16_to_int8(out, input, scale):
+    """out[int8 ..,K], scale[fp16 tokens] <- per-token symmetric quantization of input."""
+    k = input.shape[-1]
+    m = input.numel() // k
+    with torch.cuda.device(input.device):
+        check(lib.kairos_act_quant_i8(_chk(input, torch.float16, 'input'), _chk(out, torch.int8, 'out'),
+                                      _chk(scale, torch.float16, 'scale'), m, k, stream_ptr()), 'quant_fp16_to_int8')
+
+
+def dequant_interleaved_int4_to_int8(output, input, scale, scaled_zero, group_size=128):
+    assert group_size == 128
+    n, k = output.shape
+    with torch.cuda.device(output.device):
+        check(lib.kairos_w4_to_w8(_chk(input, torch.int16, 'input'), _chk(scale, torch.float16, 'scale'),
+                                  _chk(scaled_zero, torch.float16, 'scaled_zero'), _chk(output, torch.int8, 'output'),
+                                  n, k, stream_ptr()), 'dequant_interleaved_int4_to_int8')
+
+
+def dequant_interleaved_int4_to_fp16(output, input, scale, scaled_zero, group_size=128):
+    assert group_size == 128
+    n, k = output.shape
+    with torch.cuda.device(output.device):
+        check(lib.kairos_w4_to_f16(_chk(input, torch.int16, 'input'), _chk(scale, torch.float16, 'scale'),
+                                   _chk(scaled_zero, torch.float16, 'scaled_zero'),
+                                   _chk(output, torch.float16, 'output'), n, k, stream_ptr()),
+              'dequant_interleaved_int4_to_fp16')
+
+
+def trans_layout_c16_to_c8_awq(qweight, n, k):
+    """AWQ interleaved int16 [N/4,K] -> QServe int8 [N,K/2]."""
+    out = torch.empty((n, k // 2), dtype=torch.int8, device=qweight.device)
+    with torch.cuda.device(qweight.device):
+        check(lib.kairos_awq_to_qserve(_chk(qweight, torch.int16, 'qweight'), out.data_ptr(), n, k, stream_ptr()),
+              'trans_layout_c16_to_c8_awq')
+    return out
+
+
+# ---- awq_backend ------------------------------------------------------------
+def _bias_ptr(bias):
+    return None if bias is None else _chk(bias, torch.float16, 'bias')
+
+
+def gemv_forward_cuda_new(in_feats, kernel, scaling_factors, zeros, m, n, k, group_size=128, bias=None):
+    assert group_size == 128
+    x = in_feats.reshape(-1, k)
+    out = torch.empty((m, n), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.kairos_w4a16_gemv(_chk(x, torch.float16, 'in_feats'), _chk(kernel, torch.int16, 'kernel'),
+                                    _chk(scaling_factors, torch.float16, 'scaling_factors'),
+                                    _chk(zeros, torch.float16, 'zeros'), _bias_ptr(bias), out.data_ptr(), m, n, k,
+                                    stream_ptr()), 'gemv_forward_cuda_new')
+    return out
+
+
+def gemm_forward_cuda_new(in_feats, kernel, scaling_factors, zeros, bias=None):
+    k = in_feats.shape[-1]
+    x = in_feats.reshape(-1, k)
+    m, n = x.shape[0], kernel.shape[0] * 4
+    out = torch.empty((m, n), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        ws = gemm_workspace(x.device, m, n, k)
+        check(lib.kairos_w4a16_gemm(_chk(x, torch.float16, 'in_feats'), _chk(kernel, torch.int16, 'kernel'),
+                                    _chk(scaling_factors, torch.float16, 'scaling_factors'),
+                                    _chk(zeros, torch.float16, 'zeros'), _bias_ptr(bias), out.data_ptr(), m, n, k,
+                                    ws.data_ptr(), ws.numel(), stream_ptr()), 'gemm_forward_cuda_new')
+    return out
+
+
+def w8a8_gemm_forward_cuda(in_feats, kernel, wscales, ascales, out_feats, bias=None, acc_out=None):
+    m, k = in_feats.shape
+    n = kernel.shape[0]
+    with torch.cuda.device(in_feats.device):
+        ws = gemm_workspace(in_feats.device, m, n, k)
+        check(lib.kairos_w8a8_gemm(_chk(in_feats, torch.int8, 'in_feats'), _chk(kernel, torch.int8, 'kernel'),
+                                   _chk(wscales, torch.float16, 'wscales'), _chk(ascales, torch.float16, 'ascales'),
+                                   _bias_ptr(bias), _chk(out_feats, torch.float16, 'out_feats'),
+                                   None if acc_out is None else _chk(acc_out, torch.int32, 'acc_out'), m, n, k,
+                                   ws.data_ptr(), ws.numel(), stream_ptr()), 'w8a8_gemm_forward_cuda')
+    return out_feats
+
+
+# ---- kernels the reference reaches through torch / declares without a kernel ----
+def f16_gemm(x, w16, bias=None):
+    """``input @ weight.T`` with fp32 accumulation (kairos/dynamic_linear.py:163)."""
+    m, k = x.shape
+    n = w16.shape[0]
+    out = torch.empty((m, n), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        ws = gemm_workspace(x.device, m, n, k)
+        check(lib.kairos_f16_gemm(_chk(x, torch.float16, 'x'), _chk(w16, torch.float16, 'w16'), _bias_ptr(bias),
+                                  out.data_ptr(), m, n, k, ws.data_ptr(), ws.numel(), stream_ptr()), 'f16_gemm')
+    return out
+
+
+def w8a16_gemm(x, w8, wscales, bias=None):
+    """Kernel id 3: fp16 activations times the int8 weight widened to fp16 * s1."""
+    m, k = x.shape
+    n = w8.shape[0]
+    out = torch.empty((m, n), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        ws = gemm_workspace(x.device, m, n, k)
+        check(lib.kairos_w8a16_gemm(_chk(x, torch.float16, 'x'), _chk(w8, torch.int8, 'w8'),
+                                    _chk(wscales, torch.float16, 'wscales'), _bias_ptr(bias), out.data_ptr(), m, n, k,
+                                    ws.data_ptr(), ws.numel(), stream_ptr()), 'w8a16_gemm')
+    return out
