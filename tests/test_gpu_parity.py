@@ -218,6 +218,16 @@ def test_full_size_sampled_columns(kb, m, k, n):
 
 
 # ------------------------------------------------------------------ module level
+@pytest.mark.parametrize('path', SMALL, ids=[os.path.basename(p)[6:-4] for p in SMALL])
+def test_from_module_on_gpu_matches_reference(kb, path):
+    """Weight preparation run with CUDA tensors gives the reference's CPU bits."""
+    kairos_b200, _, _ = kb
+    g = dict(np.load(path))
+    layer = _layer(kairos_b200, g['W'], g.get('bias'))
+    for key in ('qweight', 'scales', 'scaled_zeros', 'scales_to8', 'scaled_zeros_to8', 'scales_1'):
+        assert np.array_equal(bits(getattr(layer, key).cpu().numpy()), bits(g[key])), key
+
+
 def _layer(kairos_b200, w, bias=None, cls=None):
     n, k = w.shape
     lin = torch.nn.Linear(k, n, bias=bias is not None, dtype=torch.float16)
