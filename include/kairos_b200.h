@@ -53,6 +53,9 @@ const char* kairos_last_error(void);
 /* Status word the kernels raise when one of their bounded waits runs out (current device).
  * Read it after synchronising; clear != 0 resets it.  KAIROS_OK or KAIROS_ERR_DEVICE. */
 int kairos_device_status(int clear);
+/* Diagnostic (no counterpart in the reference): device buffer of 64 x 8 int64 that CTA 0 of the
+ * tensor-core GEMMs fills with per-k-block clock64 stamps of its pipeline roles; null = off. */
+void kairos_debug_trace(void* device_buffer);
 
 /* ---- primitive kernels -------------------------------------------------- */
 
@@ -85,13 +88,12 @@ int kairos_awq_to_qserve(const void* qweight, void* out_i8, int N, int K, kairos
 int kairos_w4a16_gemv(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
                       const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, kairos_stream_t stream);
 
-/* Bytes of scratch the tensor-core GEMMs need for (M,N,K): split-K partial tiles and
- * tile counters.  The first KAIROS_GEMM_COUNTER_BYTES of the workspace must be zero
- * before the first call; the kernels leave them zero again. */
-#define KAIROS_GEMM_COUNTER_BYTES 16384
+/* Bytes of scratch the tensor-core GEMMs need for (M,N,K): the split-K partial tiles (0 when
+ * the problem is not split; then `workspace` may be null).  Contents need no initialisation.
+ * Calls that share a workspace must be ordered (same stream). */
 size_t kairos_gemm_workspace_bytes(int M, int N, int K);
 
-/* Y = X . dequant(W)^T (+bias): tcgen05 f16 MMA, uint4 dequantized in shared memory.
+/* Y = X . dequant(W)^T (+bias): tcgen05 f16 MMA, uint4 dequantized in shared memory (N % 8 == 0).
  * Replaces gemm_forward_cuda_new
  * (thirdparty/AWQ/kernels/csrc/quantization_new/gemm/gemm_cuda.cu:1126-1236). */
 int kairos_w4a16_gemm(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,

@@ -1,6 +1,8 @@
 """Build libkairos_b200.so in-tree with nvcc for sm_100a (no JIT cache, no pip install).
 
-    python -m kairos_b200.build [--force] [--verbose]
+    python kairos_b200/build.py [--force] [--verbose]
+
+(run it as a script: `python -m kairos_b200.build` would import the package, which needs the library)
 """
 from __future__ import annotations
 

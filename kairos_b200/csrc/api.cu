@@ -77,7 +77,7 @@ struct Ctx {
     size_t transient_bytes = 0;
     void* act_ws = nullptr;      // Xq [M,K] int8 followed by sx [M] fp16
     size_t act_bytes = 0;
-    void* gemm_ws = nullptr;     // tile counters + split-K partial tiles
+    void* gemm_ws = nullptr;     // split-K partial tiles
     size_t gemm_bytes = 0;
     void* host_x = nullptr;      // device staging for the host-buffer entry point
     void* host_y = nullptr;
@@ -107,12 +107,8 @@ static int grow(void** ptr, size_t* have, size_t need) {
 static int ensure_gemm_ws(Ctx* c, int M, int N, int K, cudaStream_t st) {
     const size_t need = gemm_workspace_bytes(M, N, K);
     if (c->gemm_bytes >= need) return KAIROS_OK;
-    const int rc = grow(&c->gemm_ws, &c->gemm_bytes, need);
-    if (rc != KAIROS_OK) return rc;
-    KAIROS_CUDA_OK(cudaMemsetAsync(c->gemm_ws, 0, KAIROS_GEMM_COUNTER_BYTES, st));
-    // other streams that use the context later must see the cleared counters
-    KAIROS_CUDA_OK(cudaStreamSynchronize(st));
-    return KAIROS_OK;
+    (void)st;
+    return grow(&c->gemm_ws, &c->gemm_bytes, need);
 }
 
 static size_t act_ws_bytes(int M, int K) { return (((size_t)M * K + 255) & ~(size_t)255) + (size_t)M * 2 + 256; }
@@ -355,12 +351,7 @@ int kairos_ctx_reserve(kairos_ctx* ctx, int max_M, int max_N, int max_K) {
     const int probes[] = {16, 32, 64, 128, 256, 512, 1024, max_M};
     for (int m : probes)
         if (m <= max_M) need = std::max(need, kairos::gemm_workspace_bytes(m, max_N, max_K));
-    if (c->gemm_bytes < need) {
-        rc = kairos::grow(&c->gemm_ws, &c->gemm_bytes, need);
-        if (rc != KAIROS_OK) return rc;
-        KAIROS_CUDA_OK(cudaMemset(c->gemm_ws, 0, KAIROS_GEMM_COUNTER_BYTES));
-    }
-    return KAIROS_OK;
+    return kairos::grow(&c->gemm_ws, &c->gemm_bytes, need);
 }
 
 int kairos_ctx_stats(const kairos_ctx* ctx, uint64_t* hits, uint64_t* misses, uint64_t* evictions,

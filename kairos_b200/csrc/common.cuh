@@ -68,6 +68,19 @@ __device__ __forceinline__ void dequant_chunk32(const uint4& raw, __half2 s, __h
     }
 }
 
+// Same expansion with q*s+z as ONE fused multiply-add (one rounding).  Used where the fp16
+// weight only feeds a tolerance-checked GEMM and instruction count matters.
+__device__ __forceinline__ void dequant_chunk32_fma(const uint4& raw, __half2 s, __half2 z, __half2 (&out)[16]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        __half2 h[4];
+        unpack8(w[c], h);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) out[4 * b + c] = __hfma2(h[b], s, z);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // shared-memory / mbarrier / TMA / tcgen05 wrappers
 // ---------------------------------------------------------------------------

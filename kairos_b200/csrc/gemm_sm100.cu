@@ -18,8 +18,8 @@
 // (TMEM -> registers -> global), 6..13 = weight expanders (dequant modes only).
 // The accumulator is double-buffered in TMEM so the epilogue of one tile overlaps the
 // main loop of the next.  Small problems are split along K: each split writes its
-// partial tile to scratch, the last one to arrive (per-tile counters) sums the partials
-// in split order (deterministic; exact for int32) and runs the epilogue.
+// partial tile to scratch and a second, grid-wide kernel sums the partials in split
+// order (deterministic; exact for int32) and runs the epilogue.
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises a status word and drains.
 #include <cuda.h>
@@ -36,7 +36,9 @@ constexpr int kTileN = 128;           // weight rows per tile (UMMA M)
 constexpr int kRowBytes = 128;        // K extent of one pipeline stage, in bytes of the MMA operand
 constexpr int kATileBytes = kTileN * kRowBytes;
 constexpr int kNumExpandWarps = 8;
-constexpr int kSmemBudget = 200 * 1024;
+constexpr int kExpandGroups = 4;                                   // k blocks expanded concurrently
+constexpr int kExpandGroupWarps = kNumExpandWarps / kExpandGroups;
+constexpr int kSmemBudget = 224 * 1024;      // of the 227 KB a CTA may use; barriers and alignment slack come on top
 
 struct GemmParams {
     int M, N, K;
@@ -48,17 +50,27 @@ struct GemmParams {
     const __half* bias;          // [N] or null
     __half* Y;                   // [M, N]
     int32_t* acc_dbg;            // [M, N] or null (int8 only)
-    uint32_t* partials;          // split-K partial tiles
-    unsigned* counters;          // four per output tile (one per 32-row quarter), zero between calls
+    uint32_t* partials;          // split-K partial tiles [tile][split][BT][128]
     int* status;                 // raised on a bounded wait that ran out
+    long long* trace;            // diagnostic: per-k-block clock64 stamps of CTA 0 (null = off)
 };
+
+constexpr int kTraceSlots = 8;     // stamps per k block: see trace_stamp() call sites
+constexpr int kTraceBlocks = 64;   // k blocks recorded
+__device__ __forceinline__ void trace_stamp(const GemmParams& p, uint32_t i, int slot) {
+    if (p.trace && blockIdx.x == 0 && i < kTraceBlocks) p.trace[i * kTraceSlots + slot] = clock64();
+}
 
 template <bool kInt8, int kMode, int BT>
 struct GemmCfg {
     static constexpr int kXTileBytes = BT * kRowBytes;
-    static constexpr int kRawBytes = kMode == kModeW4 ? 32 * 128 : (kMode == kModeW8 ? kTileN * 64 : kATileBytes);
+    // W4: packed tile (4096) + scale tile (256) + scaled-zero tile (256), padded to keep X 1024-aligned
+    static constexpr int kRawBytes = kMode == kModeW4 ? 32 * 128 + 1024 : (kMode == kModeW8 ? kTileN * 64 : kATileBytes);
+    static constexpr int kRawTxBytes = kMode == kModeW4 ? 32 * 128 + 512 : kRawBytes;
     static constexpr int kStageBytes = kRawBytes + kXTileBytes;
-    static constexpr int kAStages = kMode == kModeTma ? 0 : (BT == 256 ? 3 : 4);
+    static constexpr int kStageTxBytes = kRawTxBytes + kXTileBytes;
+    // one expanded-operand slot per expander group: a slot is always refilled by the same group, in order
+    static constexpr int kAStages = kMode == kModeTma ? 0 : kExpandGroups;
     static constexpr int kStagesFit = (kSmemBudget - kAStages * kATileBytes) / kStageBytes;
     static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
     static constexpr int kBlockK = kInt8 ? 128 : 64;          // elements of K per stage
@@ -67,6 +79,7 @@ struct GemmCfg {
     static constexpr int kBarBytes = 8 * (2 * kStages + 2 * (kAStages ? kAStages : 1) + 4) + 64;
     static constexpr int kSmemBytes = kStages * kStageBytes + kAStages * kATileBytes + kBarBytes + 1024;
     static_assert(kStages >= 2, "pipeline too shallow");
+    static_assert(kSmemBytes <= 227 * 1024, "exceeds the shared memory a CTA may use");
     static_assert(kRawBytes % 1024 == 0 && kXTileBytes % 1024 == 0, "operand tiles must stay 1024-byte aligned");
     // instruction descriptor: D format (bits 4-5), A/B formats (7-9, 10-12), K-major both,
     // N >> 3 at bit 17, M >> 4 at bit 24
@@ -85,9 +98,64 @@ __device__ __forceinline__ void widen_s8x4(uint32_t w, __half2 s, __half2& lo, _
     hi = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p1), k1152), s);
 }
 
+
+// One output element: scale (int8), round to fp16, add bias, store.
+//   int8: half(float(acc) * (float(s1[n]) * float(sx[m])))
+//         (thirdparty/AWQ/kernels/csrc/w8a8/w8a8_gemm_cuda.cu:896-901)
+template <bool kInt8>
+__device__ __forceinline__ void store_output(const GemmParams& p, uint32_t v, int m, int n, float s1f, bool has_bias,
+                                             __half bias_n) {
+    __half y;
+    if constexpr (kInt8) {
+        const float sc = __fmul_rn(s1f, __half2float(__ldg(p.sx + m)));
+        y = __float2half_rn(__fmul_rn((float)(int32_t)v, sc));
+        if (p.acc_dbg) p.acc_dbg[(size_t)m * p.N + n] = (int32_t)v;
+    } else {
+        y = __float2half_rn(__uint_as_float(v));
+    }
+    if (has_bias) y = __hadd(y, bias_n);
+    p.Y[(size_t)m * p.N + n] = y;
+}
+
+// Split-K second pass: sums the partial tiles of every output tile in split order and runs the
+// epilogue.  One CTA per (tile, token column), one thread per weight row: every load is a coalesced
+// 512-byte row of a partial tile, and the loads of a thread (one per split) are independent.
+template <bool kInt8>
+__global__ void __launch_bounds__(kTileN) splitk_reduce_kernel(const GemmParams p, int bt) {
+    const int tile = blockIdx.x / bt, c = blockIdx.x % bt;
+    const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+    const int n = n_tile * kTileN + threadIdx.x;
+    const int m = m_tile * bt + c;
+    if (n >= p.N || m >= p.M) return;
+    const uint32_t* base = p.partials + ((size_t)tile * p.splits * bt + c) * kTileN + threadIdx.x;
+    uint32_t acc = kInt8 ? 0u : __float_as_uint(0.f);
+    int sp = 0;
+    for (; sp + 4 <= p.splits; sp += 4) {
+        uint32_t v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = __ldcg(base + (size_t)(sp + u) * bt * kTileN);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if constexpr (kInt8) acc = (uint32_t)((int32_t)acc + (int32_t)v[u]);
+            else acc = __float_as_uint(__fadd_rn(__uint_as_float(acc), __uint_as_float(v[u])));
+        }
+    }
+    for (; sp < p.splits; ++sp) {
+        const uint32_t v = __ldcg(base + (size_t)sp * bt * kTileN);
+        if constexpr (kInt8) acc = (uint32_t)((int32_t)acc + (int32_t)v);
+        else acc = __float_as_uint(__fadd_rn(__uint_as_float(acc), __uint_as_float(v)));
+    }
+    float s1f = 0.f;
+    if constexpr (kInt8) s1f = __half2float(__ldg(p.s1 + n));
+    const bool has_bias = p.bias != nullptr;
+    const __half bias_n = has_bias ? __ldg(p.bias + n) : __float2half_rn(0.f);
+    store_output<kInt8>(p, acc, m, n, s1f, has_bias, bias_n);
+}
+
 template <bool kInt8, int kMode, int BT>
 __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
     umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                     const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_z,
                      const GemmParams p) {
     using Cfg = GemmCfg<kInt8, kMode, BT>;
     constexpr int kStages = Cfg::kStages;
@@ -113,10 +181,10 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kExpand ? 1 + kNumExpandWarps : 1);
+            mbar_init(&empty[s], kExpand ? 1 + kExpandGroupWarps : 1);
         }
         for (int s = 0; s < kAStages; ++s) {
-            mbar_init(&a_full[s], kNumExpandWarps);
+            mbar_init(&a_full[s], kExpandGroupWarps);
             mbar_init(&a_empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -143,7 +211,7 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             int s = 0;
-            uint32_t phase = 0;
+            uint32_t phase = 0, ti = 0;
             bool ok = true;
             for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
                 const int split = unit % p.splits;
@@ -154,14 +222,18 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* st = stage_base + s * Cfg::kStageBytes;
-                    mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
-                    if constexpr (kMode == kModeW4)        // qweight [N/4, K] int16, box 64 x 32
+                    mbar_arrive_expect_tx(&full[s], Cfg::kStageTxBytes);
+                    if constexpr (kMode == kModeW4) {      // qweight [N/4, K] int16, box 64 x 32
                         tma_load_2d(st, &tmap_w, &full[s], kb * 64, n_tile * (kTileN / kInterleave));
-                    else if constexpr (kMode == kModeW8)   // W8 [N, K] int8, box 64 x 128
+                        // factors [G, N] fp16, box 128 x 1: this tile's rows, this k block's group
+                        tma_load_2d(st + 4096, &tmap_s, &full[s], n_tile * kTileN, kb >> 1);
+                        tma_load_2d(st + 4096 + 256, &tmap_z, &full[s], n_tile * kTileN, kb >> 1);
+                    } else if constexpr (kMode == kModeW8)   // W8 [N, K] int8, box 64 x 128
                         tma_load_2d(st, &tmap_w, &full[s], kb * 64, n_tile * kTileN);
                     else                                   // [N, K], box 128 bytes x 128
                         tma_load_2d(st, &tmap_w, &full[s], kb * Cfg::kBlockK, n_tile * kTileN);
                     tma_load_2d(st + Cfg::kRawBytes, &tmap_x, &full[s], kb * Cfg::kBlockK, m_tile * BT);
+                    trace_stamp(p, ti++, 0);
                     if (++s == kStages) { s = 0; phase ^= 1; }
                 }
             }
@@ -170,7 +242,7 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
             int s = 0, as = 0, it = 0;
-            uint32_t phase = 0, aphase = 0;
+            uint32_t phase = 0, aphase = 0, ti = 0;
             bool ok = true;
             for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++it) {
                 const int split = unit % p.splits;
@@ -182,8 +254,10 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * BT);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full[s], phase, abort_flag)) { ok = false; break; }
+                    trace_stamp(p, ti, 1);
                     if constexpr (kExpand)
                         if (!mbar_wait(&a_full[as], aphase, abort_flag)) { ok = false; break; }
+                    trace_stamp(p, ti, 2);
                     tc_fence_after();
                     uint8_t* st = stage_base + s * Cfg::kStageBytes;
                     const uint32_t a_addr = kExpand ? smem_u32(a_ring + as * kATileBytes) : smem_u32(st);
@@ -193,6 +267,7 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                     for (int j = 0; j < 4; ++j)   // 4 x (K = 32 bytes) per 128-byte row; +2 = 32 bytes >> 4
                         umma<kInt8>(d_tmem, adesc + 2 * j, bdesc + 2 * j, Cfg::kIdesc, (kb > kb0 || j > 0) ? 1u : 0u);
                     umma_commit(&empty[s]);
+                    trace_stamp(p, ti++, 3);
                     if constexpr (kExpand) {
                         umma_commit(&a_empty[as]);
                         if (++as == kAStages) { as = 0; aphase ^= 1; }
@@ -220,19 +295,7 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
             const __half bias_n = (has_bias && n_ok) ? __ldg(p.bias + n) : __float2half_rn(0.f);
 
             auto finalize = [&](uint32_t v, int m) {
-                if (!n_ok || m >= p.M) return;
-                __half y;
-                if constexpr (kInt8) {
-                    // half(float(acc) * (float(s1[n]) * float(sx[m])))
-                    // (thirdparty/AWQ/kernels/csrc/w8a8/w8a8_gemm_cuda.cu:896-901)
-                    const float sc = __fmul_rn(s1f, __half2float(__ldg(p.sx + m)));
-                    y = __float2half_rn(__fmul_rn((float)(int32_t)v, sc));
-                    if (p.acc_dbg) p.acc_dbg[(size_t)m * p.N + n] = (int32_t)v;
-                } else {
-                    y = __float2half_rn(__uint_as_float(v));
-                }
-                if (has_bias) y = __hadd(y, bias_n);
-                p.Y[(size_t)m * p.N + n] = y;
+                if (n_ok && m < p.M) store_output<kInt8>(p, v, m, n, s1f, has_bias, bias_n);
             };
 
             if (!mbar_wait(&tmem_full[b], (it >> 1) & 1, abort_flag)) { ok = false; break; }
@@ -255,57 +318,27 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[b]);
-
-            if (p.splits > 1) {
-                // Publish this warp's 32-row slice of the partial tile; the warp of the split that
-                // arrives last (per (tile, quarter) counter) sums the slices in split order.  Each
-                // quarter is independent, so no cross-warp barrier is involved.
-                __threadfence();
-                __syncwarp();
-                unsigned prev = 0;
-                if (lane == 0) prev = atomicAdd(p.counters + 4 * tile + q, 1u);
-                prev = __shfl_sync(0xffffffffu, prev, 0);
-                if (prev == (unsigned)p.splits - 1u) {
-                    __threadfence();
-                    const uint32_t* base = p.partials + ((size_t)tile * p.splits * BT) * kTileN + row;
-#pragma unroll 1
-                    for (int c = 0; c < BT; ++c) {
-                        uint32_t v;
-                        if constexpr (kInt8) {
-                            int32_t acc = 0;
-                            for (int sp = 0; sp < p.splits; ++sp)
-                                acc += (int32_t)__ldcg(base + ((size_t)sp * BT + c) * kTileN);
-                            v = (uint32_t)acc;
-                        } else {
-                            float acc = 0.f;
-                            for (int sp = 0; sp < p.splits; ++sp)
-                                acc += __uint_as_float(__ldcg(base + ((size_t)sp * BT + c) * kTileN));
-                            v = __float_as_uint(acc);
-                        }
-                        finalize(v, m_tile * BT + c);
-                    }
-                    __syncwarp();
-                    if (lane == 0) p.counters[4 * tile + q] = 0u;   // ready for the next call
-                }
-            }
         }
     } else if constexpr (kExpand) {
         // ------------------------------ weight expanders --------------------------
-        const int j = threadIdx.x - 192;            // 0..255
-        int n_local, khalf;
-        if constexpr (kMode == kModeW4) {
-            // 16-byte chunk j of the [32][128 B] packed tile: qweight row j/8, weight row
-            // 4*(j/8) + (j%8)/2, k half j%2 (32 consecutive k)
-            n_local = 4 * (j >> 3) + ((j & 7) >> 1);
-            khalf = j & 1;
-        } else {
-            n_local = j >> 1;                       // [128][64 B] int8 tile: row j/2, 32 bytes each
-            khalf = j & 1;
+        // Four groups of two warps; group g expands every fourth k block (four 16-byte chunks per
+        // thread), so four k blocks are in flight and the per-block latency chain
+        // (wait -> load -> expand -> store -> fence -> arrive) is overlapped instead of serialised.
+        const int grp = (warp - 6) / kExpandGroupWarps;
+        const int t = threadIdx.x - 192 - grp * (32 * kExpandGroupWarps);     // 0..63
+        constexpr int kChunks = 256 / (32 * kExpandGroupWarps);               // chunks per thread: 4
+        int n_local[kChunks];
+        uint32_t dst_off[kChunks];
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const int j = t + 32 * kExpandGroupWarps * c;
+            // W4: 16-byte chunk j of the [32][128 B] packed tile = weight row 4*(j/8) + (j%8)/2,
+            //     k half j%2 (32 consecutive k).  W8: [128][64 B] int8 tile, row j/2, half j%2.
+            n_local[c] = kMode == kModeW4 ? 4 * (j >> 3) + ((j & 7) >> 1) : (j >> 1);
+            dst_off[c] = (uint32_t)((n_local[c] >> 3) * 1024 + (n_local[c] & 7) * 128);
         }
-        const int swz = n_local & 7;
-        const uint32_t dst_row = (uint32_t)((n_local >> 3) * 1024 + swz * 128);
-        int s = 0, as = 0;
-        uint32_t phase = 0, aphase = 0;
+        const int khalf = t & 1;                     // same for all chunks of a thread (stride is even)
+        uint32_t i = 0;                              // running k-block count of this CTA
         bool ok = true;
         for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
             const int split = unit % p.splits;
@@ -313,69 +346,73 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
             const int n_tile = tile / p.m_tiles;
             const int kb0 = split * p.kb_per_split;
             const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-            const int n = n_tile * kTileN + n_local;
-            const bool n_ok = n < p.N;
-            const __half hzero = __float2half_rn(0.f);
-            __half sc_cur = hzero, zc_cur = hzero, sc_nxt = hzero, zc_nxt = hzero;
-            int g_cur = -1;
-            if constexpr (kMode == kModeW8) sc_cur = n_ok ? __ldg(p.s1 + n) : hzero;
-            for (int kb = kb0; kb < kb1; ++kb) {
-                if constexpr (kMode == kModeW4) {
-                    const int g = kb >> 1;          // 64-wide k blocks, groups of 128
-                    if (g != g_cur) {
-                        if (g_cur < 0) {
-                            sc_cur = n_ok ? __ldg(p.scales + (size_t)g * p.N + n) : hzero;
-                            zc_cur = n_ok ? __ldg(p.scaled_zeros + (size_t)g * p.N + n) : hzero;
-                        } else {
-                            sc_cur = sc_nxt;
-                            zc_cur = zc_nxt;
-                        }
-                        g_cur = g;
-                        const bool more = n_ok && (2 * (g + 1) < kb1);
-                        sc_nxt = more ? __ldg(p.scales + (size_t)(g + 1) * p.N + n) : hzero;
-                        zc_nxt = more ? __ldg(p.scaled_zeros + (size_t)(g + 1) * p.N + n) : hzero;
-                    }
+            __half2 s8[kChunks];
+            if constexpr (kMode == kModeW8) {
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c) {
+                    const int n = n_tile * kTileN + n_local[c];
+                    s8[c] = __half2half2(n < p.N ? __ldg(p.s1 + n) : __float2half_rn(0.f));
                 }
+            }
+            for (int kb = kb0; kb < kb1; ++kb, ++i) {
+                const int s = (int)(i % kStages), as = (int)(i % kAStages);
+                const uint32_t phase = (i / kStages) & 1u, aphase = (i / kAStages) & 1u;
+                // Every group observes every stage fill, in order, also those it does not expand: a
+                // parity wait is only valid while the waiter is at most one phase away from the barrier.
                 if (!mbar_wait(&full[s], phase, abort_flag)) { ok = false; break; }
+                if ((int)(i % kExpandGroups) != grp) continue;
+                if (t == 0) trace_stamp(p, i, 4);
                 const uint8_t* st = stage_base + s * Cfg::kStageBytes;
-                uint4 raw0, raw1;
-                if constexpr (kMode == kModeW4) {
-                    raw0 = *reinterpret_cast<const uint4*>(st + 16 * j);
-                } else {
-                    raw0 = *reinterpret_cast<const uint4*>(st + 32 * j);
-                    raw1 = *reinterpret_cast<const uint4*>(st + 32 * j + 16);
+                uint4 raw[kChunks], raw_hi[kChunks];
+                __half2 sc[kChunks], zc[kChunks];
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c) {
+                    const int j = t + 32 * kExpandGroupWarps * c;
+                    if constexpr (kMode == kModeW4) {
+                        raw[c] = *reinterpret_cast<const uint4*>(st + 16 * j);
+                        // this row's factors of the k block's group, staged by TMA (zero beyond N)
+                        sc[c] = __half2half2(*reinterpret_cast<const __half*>(st + 4096 + 2 * n_local[c]));
+                        zc[c] = __half2half2(*reinterpret_cast<const __half*>(st + 4096 + 256 + 2 * n_local[c]));
+                    } else {
+                        raw[c] = *reinterpret_cast<const uint4*>(st + 32 * j);
+                        raw_hi[c] = *reinterpret_cast<const uint4*>(st + 32 * j + 16);
+                    }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);           // packed tile is in registers
-                if (++s == kStages) { s = 0; phase ^= 1; }
-
-                __half2 w[16];
-                if constexpr (kMode == kModeW4) {
-                    dequant_chunk32(raw0, __half2half2(sc_cur), __half2half2(zc_cur), w);
-                } else {
-                    const __half2 s2 = __half2half2(sc_cur);
-                    widen_s8x4(raw0.x, s2, w[0], w[1]);
-                    widen_s8x4(raw0.y, s2, w[2], w[3]);
-                    widen_s8x4(raw0.z, s2, w[4], w[5]);
-                    widen_s8x4(raw0.w, s2, w[6], w[7]);
-                    widen_s8x4(raw1.x, s2, w[8], w[9]);
-                    widen_s8x4(raw1.y, s2, w[10], w[11]);
-                    widen_s8x4(raw1.z, s2, w[12], w[13]);
-                    widen_s8x4(raw1.w, s2, w[14], w[15]);
-                }
+                if (t == 0) trace_stamp(p, i, 5);
                 if (!mbar_wait(&a_empty[as], aphase ^ 1, abort_flag)) { ok = false; break; }
-                uint8_t* dst = a_ring + as * kATileBytes + dst_row;
-                const uint32_t* u = reinterpret_cast<const uint32_t*>(w);
+                if (t == 0) trace_stamp(p, i, 6);
+                uint8_t* a_tile = a_ring + as * kATileBytes;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int chunk = (4 * khalf + i) ^ swz;    // 128-byte swizzle: 16-byte chunk ^ (row % 8)
-                    *reinterpret_cast<uint4*>(dst + 16 * chunk) =
-                        make_uint4(u[4 * i], u[4 * i + 1], u[4 * i + 2], u[4 * i + 3]);
+                for (int c = 0; c < kChunks; ++c) {
+                    __half2 w[16];
+                    if constexpr (kMode == kModeW4) {
+                        dequant_chunk32_fma(raw[c], sc[c], zc[c], w);
+                    } else {
+                        widen_s8x4(raw[c].x, s8[c], w[0], w[1]);
+                        widen_s8x4(raw[c].y, s8[c], w[2], w[3]);
+                        widen_s8x4(raw[c].z, s8[c], w[4], w[5]);
+                        widen_s8x4(raw[c].w, s8[c], w[6], w[7]);
+                        widen_s8x4(raw_hi[c].x, s8[c], w[8], w[9]);
+                        widen_s8x4(raw_hi[c].y, s8[c], w[10], w[11]);
+                        widen_s8x4(raw_hi[c].z, s8[c], w[12], w[13]);
+                        widen_s8x4(raw_hi[c].w, s8[c], w[14], w[15]);
+                    }
+                    uint8_t* dst = a_tile + dst_off[c];
+                    const int swz = n_local[c] & 7;
+                    const uint32_t* u = reinterpret_cast<const uint32_t*>(w);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const int chunk = (4 * khalf + q4) ^ swz;   // 128-byte swizzle: 16-byte chunk ^ (row % 8)
+                        *reinterpret_cast<uint4*>(dst + 16 * chunk) =
+                            make_uint4(u[4 * q4], u[4 * q4 + 1], u[4 * q4 + 2], u[4 * q4 + 3]);
+                    }
                 }
                 fence_proxy_async_smem();                        // generic-proxy writes -> visible to the MMA
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&a_full[as]);
-                if (++as == kAStages) { as = 0; aphase ^= 1; }
+                if (t == 0) trace_stamp(p, i, 7);
             }
         }
     }
@@ -445,6 +482,8 @@ int device_sm_count() {
 
 int* device_status_word();   // api.cu: host-mapped word the kernels raise on a timed-out wait
 
+static long long* g_trace = nullptr;   // diagnostic buffer of kTraceBlocks * kTraceSlots stamps, or null
+
 static int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
 struct Plan {
@@ -474,9 +513,9 @@ static Plan make_plan(int M, int N, int K, bool int8) {
 }
 
 size_t gemm_workspace_bytes(int M, int N, int K) {
-    if (M <= 0 || N <= 0 || K <= 0) return KAIROS_GEMM_COUNTER_BYTES;
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
     const Plan a = make_plan(M, N, K, false), b = make_plan(M, N, K, true);
-    return KAIROS_GEMM_COUNTER_BYTES + (a.partial_bytes > b.partial_bytes ? a.partial_bytes : b.partial_bytes);
+    return a.partial_bytes > b.partial_bytes ? a.partial_bytes : b.partial_bytes;
 }
 
 struct GemmArgs {
@@ -494,12 +533,19 @@ struct GemmArgs {
 template <bool kInt8, int kMode, int BT>
 static int launch_one(const GemmArgs& a, const Plan& pl) {
     using Cfg = GemmCfg<kInt8, kMode, BT>;
-    CUtensorMap tw, tx;
+    CUtensorMap tw, tx, ts, tz;
     int rc;
-    if constexpr (kMode == kModeW4)
+    if constexpr (kMode == kModeW4) {
         rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)a.N / kInterleave, (uint64_t)a.K, 64, 32,
                        false);
-    else if constexpr (kMode == kModeW8)
+        if (rc != KAIROS_OK) return rc;
+        // factor tensors [K/128 used rows, N] fp16: one 128-wide row slice per (tile, group)
+        rc = make_tmap(&ts, a.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.K / kGroup, (uint64_t)a.N,
+                       kTileN, 1, false);
+        if (rc != KAIROS_OK) return rc;
+        rc = make_tmap(&tz, a.scaled_zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.K / kGroup, (uint64_t)a.N,
+                       kTileN, 1, false);
+    } else if constexpr (kMode == kModeW8)
         rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.N, (uint64_t)a.K, 64, kTileN, false);
     else if constexpr (kInt8)
         rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.N, (uint64_t)a.K, 128, kTileN, true);
@@ -511,6 +557,10 @@ static int launch_one(const GemmArgs& a, const Plan& pl) {
     else
         rc = make_tmap(&tx, a.X, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.M, (uint64_t)a.K, 64, BT, true);
     if (rc != KAIROS_OK) return rc;
+    if constexpr (kMode != kModeW4) {
+        ts = tx;   // unused by the kernel in these modes
+        tz = tx;
+    }
 
     GemmParams p;
     p.M = a.M; p.N = a.N; p.K = a.K;
@@ -519,9 +569,9 @@ static int launch_one(const GemmArgs& a, const Plan& pl) {
     p.scales = a.scales; p.scaled_zeros = a.scaled_zeros; p.s1 = a.s1; p.sx = a.sx; p.bias = a.bias;
     p.Y = static_cast<__half*>(a.Y);
     p.acc_dbg = static_cast<int32_t*>(a.acc_dbg);
-    p.counters = static_cast<unsigned*>(a.workspace);
-    p.partials = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(a.workspace) + KAIROS_GEMM_COUNTER_BYTES);
+    p.partials = static_cast<uint32_t*>(a.workspace);
     p.status = device_status_word();
+    p.trace = g_trace;
     if (!p.status) return KAIROS_ERR_CUDA;
 
     static bool attr_set = false;    // per instantiation
@@ -533,7 +583,12 @@ static int launch_one(const GemmArgs& a, const Plan& pl) {
     const int units = pl.n_tiles * pl.m_tiles * pl.splits;
     const int sms = device_sm_count();
     const int grid = units < sms ? units : sms;
-    umma_gemm_kernel<kInt8, kMode, BT><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(tw, tx, p);
+    umma_gemm_kernel<kInt8, kMode, BT><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(tw, tx, ts, tz, p);
+    if (pl.splits > 1) {
+        const int rc2 = launch_status();
+        if (rc2 != KAIROS_OK) return rc2;
+        splitk_reduce_kernel<kInt8><<<pl.n_tiles * pl.m_tiles * BT, kTileN, 0, a.stream>>>(p, BT);
+    }
     return launch_status();
 }
 
@@ -543,11 +598,9 @@ int launch_gemm(const GemmArgs& a) {
     if (a.M == 0) return KAIROS_OK;
     if (!a.X || !a.W || !a.Y || ((uintptr_t)a.X & 15) || ((uintptr_t)a.W & 15) || ((uintptr_t)a.Y & 1))
         return KAIROS_ERR_ALIGN;
+    if (kMode == kModeW4 && (a.N % 8) != 0) return KAIROS_ERR_SHAPE;   // factor rows must be 16-byte multiples
     const Plan pl = make_plan(a.M, a.N, a.K, kInt8);
-    if (4 * pl.n_tiles * pl.m_tiles > (int)(KAIROS_GEMM_COUNTER_BYTES / sizeof(unsigned)) && pl.splits > 1)
-        return KAIROS_ERR_WORKSPACE;
-    if (!a.workspace || ((uintptr_t)a.workspace & 15) ||
-        a.workspace_bytes < KAIROS_GEMM_COUNTER_BYTES + pl.partial_bytes)
+    if (pl.partial_bytes > 0 && (!a.workspace || ((uintptr_t)a.workspace & 15) || a.workspace_bytes < pl.partial_bytes))
         return KAIROS_ERR_WORKSPACE;
     switch (pl.bt) {
         case 16: return launch_one<kInt8, kMode, 16>(a, pl);
@@ -566,6 +619,12 @@ template int launch_gemm<false, kModeW8>(const GemmArgs&);
 }  // namespace kairos
 
 using kairos::GemmArgs;
+
+/* Diagnostic: when given a device buffer of 64 x 8 int64, CTA 0 of every tensor-core GEMM launched
+ * afterwards stamps clock64() per k block: [0] TMA issued, [1] MMA saw the stage, [2] MMA saw the
+ * expanded operand, [3] MMA committed, [4..7] expander: saw the stage / loaded / got its slot /
+ * published.  Null switches it off. */
+extern "C" void kairos_debug_trace(void* device_buffer) { kairos::g_trace = static_cast<long long*>(device_buffer); }
 
 extern "C" size_t kairos_gemm_workspace_bytes(int M, int N, int K) { return kairos::gemm_workspace_bytes(M, N, K); }
 

@@ -42,12 +42,14 @@ def test_argument_validation_needs_no_device():
     assert L.kairos_w4_to_w8(16, 16, 16, 16, 6, 128, None) == -1          # N % 4
     assert L.kairos_w4_to_f16(16, 16, 16, 16, 8, 192, None) == -1         # K % 128
     assert L.kairos_w4a16_gemv(16, 16, 16, 16, None, 16, 33, 8, 128, None) == -1   # M > 32
-    assert L.kairos_w4a16_gemm(16, 16, 16, 16, None, 16, 4, 8, 128, None, 0, None) == -4   # no workspace
+    assert L.kairos_w4a16_gemm(16, 16, 16, 16, None, 16, 4, 256, 4096, None, 0, None) == -4   # split-K, no workspace
+    assert L.kairos_w4a16_gemm(16, 16, 16, 16, None, 16, 4, 12, 128, None, 0, None) == -1     # N % 8
     assert L.kairos_w8a8_gemm(16, 16, 16, 16, None, 16, None, 4, 8, 100, 16, 1 << 20, None) == -1
     assert L.kairos_awq_to_qserve(16, 16, 48, 64, None) == -1             # N % 32
     assert L.kairos_switched_linear(None, 16, 16, 1, 0, None) == -8
     assert b'kernel id' in L.kairos_status_str(-6)
-    assert L.kairos_gemm_workspace_bytes(16, 4096, 4096) >= 16384
+    assert L.kairos_gemm_workspace_bytes(16, 4096, 4096) == 4 * 32 * 16 * 128 * 4     # 4 splits x 32 tiles
+    assert L.kairos_gemm_workspace_bytes(8192, 4096, 4096) == 0
 
 
 def test_native_lut_known_answers():
