@@ -100,6 +100,20 @@ int kairos_w4a16_gemm(const void* X_f16, const void* qweight, const void* scales
                       const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, void* workspace,
                       size_t workspace_bytes, kairos_stream_t stream);
 
+/* The same W4A16 GEMM for callers that must not allocate device memory (no counterpart in the
+ * reference): the split-K scratch is a 5 MiB array built into the library image, so there is no
+ * workspace argument and the call runs no cudaMalloc/cudaFree of any kind.  Limits and rules:
+ *   - (M, N, K) whose split-K scratch exceeds 5 MiB are rejected with KAIROS_ERR_WORKSPACE
+ *     (every M <= 64 fits; larger M fits when kairos_gemm_workspace_bytes(M,N,K) <= 5 MiB);
+ *   - the first call on a device resolves the array's device address and sets kernel attributes;
+ *     make that first call outside any stream capture;
+ *   - all calls on a device share the one array: calls that may overlap on the GPU (different
+ *     streams without ordering) race on it.  Nothing in it has to start at zero: every partial
+ *     tile is written in full before it is read. */
+int kairos_w4a16_gemm_noalloc(const void* X_f16, const void* qweight, const void* scales,
+                              const void* scaled_zeros, const void* bias_f16_or_null, void* Y_f16, int M, int N,
+                              int K, kairos_stream_t stream);
+
 /* Y = X . (fp16(W8)*s1)^T (+bias): tcgen05 f16 MMA, int8 weight widened in shared memory.
  * Kernel id 3 of kairos/dynamic_linear.py:8-9 (declared there, no kernel in the reference). */
 int kairos_w8a16_gemm(const void* X_f16, const void* W8, const void* scales_1, const void* bias_f16_or_null,

@@ -28,6 +28,7 @@ SIGNATURES = {
     'kairos_w4a16_gemv': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p]),
     'kairos_gemm_workspace_bytes': (c_size_t, [c_int, c_int, c_int]),
     'kairos_w4a16_gemm': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
+    'kairos_w4a16_gemm_noalloc': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p]),
     'kairos_w8a16_gemm': (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
     'kairos_w8a8_gemm': (c_int, [c_void_p] * 7 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
     'kairos_f16_gemm': (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),

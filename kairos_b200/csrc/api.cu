@@ -24,6 +24,8 @@ int launch_status() {
     return e == cudaSuccess ? KAIROS_OK : note_cuda_error(e);
 }
 
+void set_last_error(const char* msg) { g_last_error = msg; }
+
 static int fail(int code, const char* what) {
     g_last_error = what;
     return code;

@@ -24,6 +24,7 @@ inline int padded_groups(int K) { return ((K / kGroup + 7) / 8) * 8; }
 
 int note_cuda_error(cudaError_t e);   // records the message, returns KAIROS_ERR_CUDA
 int launch_status();                  // cudaGetLastError() -> status
+void set_last_error(const char* msg); // detail text returned by kairos_last_error()
 
 // ---------------------------------------------------------------------------
 // uint4 unpack.  A 32-bit word of the base holds, for fixed (row, a, c), the

@@ -528,6 +528,7 @@ struct GemmArgs {
     void* workspace;
     size_t workspace_bytes;
     cudaStream_t stream;
+    int* status = nullptr;   // device word for timed-out waits; null = the per-device host-mapped word
 };
 
 template <bool kInt8, int kMode, int BT>
@@ -570,7 +571,7 @@ static int launch_one(const GemmArgs& a, const Plan& pl) {
     p.Y = static_cast<__half*>(a.Y);
     p.acc_dbg = static_cast<int32_t*>(a.acc_dbg);
     p.partials = static_cast<uint32_t*>(a.workspace);
-    p.status = device_status_word();
+    p.status = a.status ? a.status : device_status_word();
     p.trace = g_trace;
     if (!p.status) return KAIROS_ERR_CUDA;
 
@@ -662,4 +663,72 @@ extern "C" int kairos_f16_gemm(const void* X, const void* W16, const void* bias,
     GemmArgs a{X, W16, nullptr, nullptr, nullptr, nullptr, static_cast<const __half*>(bias), Y, nullptr, M, N, K,
                workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream)};
     return kairos::launch_gemm<false, kairos::kModeTma>(a);
+}
+
+// ---------------------------------------------------------------------------------
+// Allocation-free variant of the W4A16 tensor-core GEMM.
+//
+// Some hosts of this library may not allocate device memory at call time at all: an inference
+// server that hands the whole GPU to its own arena at start-up and forbids later cudaMalloc, a
+// real-time loop whose latency budget has no room for an allocator call, a plugin running inside
+// someone else's CUDA-graph capture.  For those callers the split-K scratch of the GEMM lives in a
+// fixed array inside the library image instead of a caller- or context-owned buffer.
+//
+// The array is device memory that every GPU which loads the library keeps until the process ends.
+// Its name is only meaningful to device code; the host asks the runtime for its device address once
+// per device (with that device current) and hands that address to the kernels like any workspace.
+// ---------------------------------------------------------------------------------
+#define KAIROS_NOALLOC_SCRATCH_BYTES (5u << 20)
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[KAIROS_NOALLOC_SCRATCH_BYTES];
+static __device__ int g_noalloc_status;   // raised by a bounded wait that ran out (starts at zero)
+
+namespace kairos {
+struct NoAllocSlot {
+    void* scratch = nullptr;
+    int* status = nullptr;
+};
+static NoAllocSlot g_noalloc_slots[64];
+static std::mutex g_noalloc_mu;
+
+// Device address of the built-in scratch on the CURRENT device, resolved on first use.
+static int noalloc_slot(NoAllocSlot* out) {
+    int dev = 0;
+    KAIROS_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return KAIROS_ERR_ARG;
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    NoAllocSlot& slot = g_noalloc_slots[dev];
+    if (!slot.scratch) {
+        void* scratch = nullptr;
+        void* status = nullptr;
+        KAIROS_CUDA_OK(cudaGetSymbolAddress(&scratch, g_noalloc_scratch));
+        KAIROS_CUDA_OK(cudaGetSymbolAddress(&status, g_noalloc_status));
+        slot.status = static_cast<int*>(status);
+        slot.scratch = scratch;
+    }
+    *out = slot;
+    return KAIROS_OK;
+}
+}  // namespace kairos
+
+extern "C" int kairos_w4a16_gemm_noalloc(const void* X, const void* qweight, const void* scales,
+                                         const void* scaled_zeros, const void* bias, void* Y, int M, int N, int K,
+                                         kairos_stream_t stream) {
+    using namespace kairos;
+    if (!scales || !scaled_zeros) return KAIROS_ERR_ALIGN;
+    if (M < 0 || N <= 0 || K <= 0 || (K % kGroup) != 0 || (N % 8) != 0) return KAIROS_ERR_SHAPE;
+    if (M == 0) return KAIROS_OK;
+    const size_t need = make_plan(M, N, K, false).partial_bytes;
+    if (need > KAIROS_NOALLOC_SCRATCH_BYTES) {
+        set_last_error("kairos_w4a16_gemm_noalloc: this (M, N, K) needs more split-K scratch than the 5 MiB built "
+                       "into the library; use kairos_w4a16_gemm with a caller-owned workspace");
+        return KAIROS_ERR_WORKSPACE;
+    }
+    NoAllocSlot slot;
+    const int rc = noalloc_slot(&slot);
+    if (rc != KAIROS_OK) return rc;
+    GemmArgs a{X, qweight, static_cast<const __half*>(scales), static_cast<const __half*>(scaled_zeros), nullptr,
+               nullptr, static_cast<const __half*>(bias), Y, nullptr, M, N, K, slot.scratch,
+               (size_t)KAIROS_NOALLOC_SCRATCH_BYTES, reinterpret_cast<cudaStream_t>(stream), slot.status};
+    return launch_gemm<false, kModeW4>(a);
 }
