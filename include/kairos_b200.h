@@ -88,6 +88,13 @@ int kairos_awq_to_qserve(const void* qweight, void* out_i8, int N, int K, kairos
 int kairos_w4a16_gemv(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
                       const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, kairos_stream_t stream);
 
+/* Same product for 1 <= M <= 16 on warp-level tensor-core instructions: the uint4 values go from
+ * registers straight into the MMA and the per-group factors are applied to the accumulators.  Serves
+ * the batch sizes where the CUDA-core kernel above is instruction-bound.  Same reference counterpart
+ * (gemv_cuda.cu:245-463, template cases Batch = 1..16). */
+int kairos_w4a16_decode(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
+                        const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, kairos_stream_t stream);
+
 /* Bytes of scratch the tensor-core GEMMs need for (M,N,K): the split-K partial tiles (0 when
  * the problem is not split; then `workspace` may be null).  Contents need no initialisation.
  * Calls that share a workspace must be ordered (same stream). */

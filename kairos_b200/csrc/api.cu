@@ -195,6 +195,10 @@ static int run_switched(Layer* L, const void* X, void* Y, int M, int comp, cudaS
     int rc;
     switch (comp) {
         case KAIROS_COMP_W4A16_GEMV:
+            // two kernels serve this id: the CUDA-core weight streamer wins for a single token on small
+            // matrices, the warp-MMA decode kernel everywhere else up to 16 tokens (measured on B200)
+            if (M <= 16 && !(M == 1 && (size_t)L->N * L->K <= (size_t)4096 * 4096))
+                return kairos_w4a16_decode(X, L->qweight, L->scales, L->scaled_zeros, L->bias, Y, M, L->N, L->K, ks);
             return kairos_w4a16_gemv(X, L->qweight, L->scales, L->scaled_zeros, L->bias, Y, M, L->N, L->K, ks);
         case KAIROS_COMP_W4A16_GEMM:
             if ((rc = ensure_gemm_ws(c, M, L->N, L->K, st)) != KAIROS_OK) return rc;

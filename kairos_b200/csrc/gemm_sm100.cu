@@ -63,24 +63,34 @@ __device__ __forceinline__ void trace_stamp(const GemmParams& p, uint32_t i, int
 
 template <bool kInt8, int kMode, int BT>
 struct GemmCfg {
-    static constexpr int kXTileBytes = BT * kRowBytes;
-    // W4: packed tile (4096) + scale tile (256) + scaled-zero tile (256), padded to keep X 1024-aligned
-    static constexpr int kRawBytes = kMode == kModeW4 ? 32 * 128 + 1024 : (kMode == kModeW8 ? kTileN * 64 : kATileBytes);
-    static constexpr int kRawTxBytes = kMode == kModeW4 ? 32 * 128 + 512 : kRawBytes;
-    static constexpr int kStageBytes = kRawBytes + kXTileBytes;
-    static constexpr int kStageTxBytes = kRawTxBytes + kXTileBytes;
+    // k blocks (128 bytes of K per operand row) moved per pipeline stage.  Issuing a TMA copy costs
+    // the issuing thread a few hundred cycles whatever its size, so small token tiles bundle four
+    // k blocks into every copy.
+    static constexpr int kSub = BT <= 64 ? 4 : (BT == 128 ? 2 : 1);
+    static constexpr int kBlockK = kInt8 ? 128 : 64;                  // elements of K per k block
+    static constexpr int kXTileBytes = BT * kRowBytes;                // per k block
+    static constexpr int kXStageBytes = kSub * kXTileBytes;
+    // weight side of a stage
+    static constexpr int kFactorGroups = kSub >= 2 ? kSub / 2 : 1;   // W4: quantization groups per stage
+    static constexpr int kPackedBytes = kSub * 32 * 128;              // W4: [32 rows][kSub x 128 B]
+    static constexpr int kWStageBytes = kMode == kModeW4 ? kPackedBytes + 1024
+                                       : kMode == kModeW8 ? kSub * kTileN * 64
+                                                          : kSub * kATileBytes;
+    static constexpr int kWTxBytes = kMode == kModeW4 ? kPackedBytes + 2 * kFactorGroups * 256 : kWStageBytes;
+    static constexpr int kStageBytes = kWStageBytes + kXStageBytes;
     // one expanded-operand slot per expander group: a slot is always refilled by the same group, in order
     static constexpr int kAStages = kMode == kModeTma ? 0 : kExpandGroups;
     static constexpr int kStagesFit = (kSmemBudget - kAStages * kATileBytes) / kStageBytes;
-    static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
-    static constexpr int kBlockK = kInt8 ? 128 : 64;          // elements of K per stage
-    static constexpr int kThreads = kMode == kModeTma ? 192 : 192 + 32 * kNumExpandWarps;
+    static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
+    static constexpr int kWarps = (kMode == kModeTma ? 6 : 6 + kNumExpandWarps) + 1;   // + activation producer
+    static constexpr int kThreads = 32 * kWarps;
     static constexpr int kTmemCols = 2 * BT < 32 ? 32 : 2 * BT;
     static constexpr int kBarBytes = 8 * (2 * kStages + 2 * (kAStages ? kAStages : 1) + 4) + 64;
     static constexpr int kSmemBytes = kStages * kStageBytes + kAStages * kATileBytes + kBarBytes + 1024;
     static_assert(kStages >= 2, "pipeline too shallow");
     static_assert(kSmemBytes <= 227 * 1024, "exceeds the shared memory a CTA may use");
-    static_assert(kRawBytes % 1024 == 0 && kXTileBytes % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+    static_assert(kWStageBytes % 1024 == 0 && kXTileBytes % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+    static_assert(kExpandGroups % kSub == 0, "a stage must hold whole expander rounds");
     // instruction descriptor: D format (bits 4-5), A/B formats (7-9, 10-12), K-major both,
     // N >> 3 at bit 17, M >> 4 at bit 24
     static constexpr uint32_t kIdesc = (kInt8 ? (2u << 4) | (1u << 7) | (1u << 10) : (1u << 4)) |
@@ -97,7 +107,6 @@ __device__ __forceinline__ void widen_s8x4(uint32_t w, __half2 s, __half2& lo, _
     lo = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p0), k1152), s);
     hi = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p1), k1152), s);
 }
-
 
 // One output element: scale (int8), round to fp16, add bias, store.
 //   int8: half(float(acc) * (float(s1[n]) * float(sx[m])))
@@ -152,6 +161,22 @@ __global__ void __launch_bounds__(kTileN) splitk_reduce_kernel(const GemmParams 
     store_output<kInt8>(p, acc, m, n, s1f, has_bias, bias_n);
 }
 
+// The k-block range of a work unit.  Ranges start and end on multiples of the stage bundle; k blocks
+// past the end of K are zero-filled by TMA and contribute nothing.
+struct UnitRange {
+    int tile, m_tile, n_tile, kb0, kb1;
+};
+__device__ __forceinline__ UnitRange unit_range(const GemmParams& p, int unit) {
+    UnitRange u;
+    const int split = unit % p.splits;
+    u.tile = unit / p.splits;
+    u.m_tile = u.tile % p.m_tiles;
+    u.n_tile = u.tile / p.m_tiles;
+    u.kb0 = split * p.kb_per_split;
+    u.kb1 = min(p.kb_total, u.kb0 + p.kb_per_split);
+    return u;
+}
+
 template <bool kInt8, int kMode, int BT>
 __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
     umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -160,6 +185,7 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
     using Cfg = GemmCfg<kInt8, kMode, BT>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kAStages = Cfg::kAStages;
+    constexpr int kSub = Cfg::kSub;
     constexpr bool kExpand = kMode != kModeTma;
 
     extern __shared__ uint8_t smem_raw[];
@@ -180,8 +206,8 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kExpand ? 1 + kExpandGroupWarps : 1);
+            mbar_init(&full[s], 2);                                   // weight producer + activation producer
+            mbar_init(&empty[s], kExpand ? 1 + kSub * kExpandGroupWarps : 1);
         }
         for (int s = 0; s < kAStages; ++s) {
             mbar_init(&a_full[s], kExpandGroupWarps);
@@ -195,6 +221,10 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
         fence_mbar_init();
         tma_prefetch_desc(&tmap_w);
         tma_prefetch_desc(&tmap_x);
+        if constexpr (kMode == kModeW4) {
+            tma_prefetch_desc(&tmap_s);
+            tma_prefetch_desc(&tmap_z);
+        }
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -208,32 +238,49 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
     const int total_units = p.n_tiles * p.m_tiles * p.splits;
 
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+        // ------------------------------ weight-side TMA producer -------------------
         if (lane == 0) {
             int s = 0;
             uint32_t phase = 0, ti = 0;
             bool ok = true;
             for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
-                const int split = unit % p.splits;
-                const int tile = unit / p.splits;
-                const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
-                const int kb0 = split * p.kb_per_split;
-                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-                for (int kb = kb0; kb < kb1; ++kb) {
+                const UnitRange u = unit_range(p, unit);
+                for (int kb = u.kb0; kb < u.kb1; kb += kSub, ti += kSub) {
                     if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* st = stage_base + s * Cfg::kStageBytes;
-                    mbar_arrive_expect_tx(&full[s], Cfg::kStageTxBytes);
-                    if constexpr (kMode == kModeW4) {      // qweight [N/4, K] int16, box 64 x 32
-                        tma_load_2d(st, &tmap_w, &full[s], kb * 64, n_tile * (kTileN / kInterleave));
-                        // factors [G, N] fp16, box 128 x 1: this tile's rows, this k block's group
-                        tma_load_2d(st + 4096, &tmap_s, &full[s], n_tile * kTileN, kb >> 1);
-                        tma_load_2d(st + 4096 + 256, &tmap_z, &full[s], n_tile * kTileN, kb >> 1);
-                    } else if constexpr (kMode == kModeW8)   // W8 [N, K] int8, box 64 x 128
-                        tma_load_2d(st, &tmap_w, &full[s], kb * 64, n_tile * kTileN);
-                    else                                   // [N, K], box 128 bytes x 128
-                        tma_load_2d(st, &tmap_w, &full[s], kb * Cfg::kBlockK, n_tile * kTileN);
-                    tma_load_2d(st + Cfg::kRawBytes, &tmap_x, &full[s], kb * Cfg::kBlockK, m_tile * BT);
-                    trace_stamp(p, ti++, 0);
+                    mbar_arrive_expect_tx(&full[s], Cfg::kWTxBytes);
+                    if constexpr (kMode == kModeW4) {
+                        // qweight [N/4, K] int16: 32 rows x (kSub x 64) columns
+                        tma_load_2d(st, &tmap_w, &full[s], kb * 64, u.n_tile * (kTileN / kInterleave));
+                        // factors [G, N] fp16: this tile's 128 rows, the stage's groups
+                        tma_load_2d(st + Cfg::kPackedBytes, &tmap_s, &full[s], u.n_tile * kTileN, kb >> 1);
+                        tma_load_2d(st + Cfg::kPackedBytes + Cfg::kFactorGroups * 256, &tmap_z, &full[s],
+                                    u.n_tile * kTileN, kb >> 1);
+                    } else if constexpr (kMode == kModeW8) {
+                        // W8 [N, K] int8: 128 rows x (kSub x 64) bytes
+                        tma_load_2d(st, &tmap_w, &full[s], kb * 64, u.n_tile * kTileN);
+                    } else {
+                        // operand tiles [k block][128 rows][128 B], swizzled
+                        tma_load_3d(st, &tmap_w, &full[s], 0, u.n_tile * kTileN, kb);
+                    }
+                    trace_stamp(p, ti, 0);
+                    if (++s == kStages) { s = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == Cfg::kWarps - 1) {
+        // ------------------------------ activation TMA producer --------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+                const UnitRange u = unit_range(p, unit);
+                for (int kb = u.kb0; kb < u.kb1; kb += kSub) {
+                    if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* st = stage_base + s * Cfg::kStageBytes + Cfg::kWStageBytes;
+                    mbar_arrive_expect_tx(&full[s], Cfg::kXStageBytes);
+                    tma_load_3d(st, &tmap_x, &full[s], 0, u.m_tile * BT, kb);   // [k block][BT rows][128 B]
                     if (++s == kStages) { s = 0; phase ^= 1; }
                 }
             }
@@ -245,33 +292,37 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
             uint32_t phase = 0, aphase = 0, ti = 0;
             bool ok = true;
             for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++it) {
-                const int split = unit % p.splits;
-                const int kb0 = split * p.kb_per_split;
-                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const UnitRange u = unit_range(p, unit);
                 const int b = it & 1;
                 if (!mbar_wait(&tmem_empty[b], ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * BT);
-                for (int kb = kb0; kb < kb1; ++kb) {
+                for (int kb = u.kb0; kb < u.kb1 && ok; kb += kSub) {
                     if (!mbar_wait(&full[s], phase, abort_flag)) { ok = false; break; }
                     trace_stamp(p, ti, 1);
-                    if constexpr (kExpand)
-                        if (!mbar_wait(&a_full[as], aphase, abort_flag)) { ok = false; break; }
-                    trace_stamp(p, ti, 2);
-                    tc_fence_after();
                     uint8_t* st = stage_base + s * Cfg::kStageBytes;
-                    const uint32_t a_addr = kExpand ? smem_u32(a_ring + as * kATileBytes) : smem_u32(st);
-                    const uint64_t adesc = umma_desc_sw128(a_addr);
-                    const uint64_t bdesc = umma_desc_sw128(smem_u32(st + Cfg::kRawBytes));
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)   // 4 x (K = 32 bytes) per 128-byte row; +2 = 32 bytes >> 4
-                        umma<kInt8>(d_tmem, adesc + 2 * j, bdesc + 2 * j, Cfg::kIdesc, (kb > kb0 || j > 0) ? 1u : 0u);
-                    umma_commit(&empty[s]);
-                    trace_stamp(p, ti++, 3);
-                    if constexpr (kExpand) {
-                        umma_commit(&a_empty[as]);
-                        if (++as == kAStages) { as = 0; aphase ^= 1; }
+                    for (int sub = 0; sub < kSub; ++sub, ++ti) {
+                        if constexpr (kExpand)
+                            if (!mbar_wait(&a_full[as], aphase, abort_flag)) { ok = false; break; }
+                        trace_stamp(p, ti, 2);
+                        tc_fence_after();
+                        const uint32_t a_addr =
+                            kExpand ? smem_u32(a_ring + as * kATileBytes) : smem_u32(st + sub * kATileBytes);
+                        const uint64_t adesc = umma_desc_sw128(a_addr);
+                        const uint64_t bdesc =
+                            umma_desc_sw128(smem_u32(st + Cfg::kWStageBytes + sub * Cfg::kXTileBytes));
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)   // 4 x (K = 32 bytes) per 128-byte row; +2 = 32 bytes >> 4
+                            umma<kInt8>(d_tmem, adesc + 2 * j, bdesc + 2 * j, Cfg::kIdesc,
+                                        (kb + sub > u.kb0 || j > 0) ? 1u : 0u);
+                        if constexpr (kExpand) {
+                            umma_commit(&a_empty[as]);
+                            if (++as == kAStages) { as = 0; aphase ^= 1; }
+                        }
+                        trace_stamp(p, ti, 3);
                     }
+                    if (ok) umma_commit(&empty[s]);
                     if (++s == kStages) { s = 0; phase ^= 1; }
                 }
                 if (ok) umma_commit(&tmem_full[b]);
@@ -284,19 +335,14 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
         int it = 0;
         bool ok = true;
         for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++it) {
-            const int tile = unit / p.splits;
-            const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
-            const int n = n_tile * kTileN + row;
+            const UnitRange u = unit_range(p, unit);
+            const int n = u.n_tile * kTileN + row;
             const bool n_ok = n < p.N;
             const int b = it & 1;
             float s1f = 0.f;
             if constexpr (kInt8) s1f = n_ok ? __half2float(__ldg(p.s1 + n)) : 0.f;
             const bool has_bias = p.bias != nullptr;
             const __half bias_n = (has_bias && n_ok) ? __ldg(p.bias + n) : __float2half_rn(0.f);
-
-            auto finalize = [&](uint32_t v, int m) {
-                if (n_ok && m < p.M) store_output<kInt8>(p, v, m, n, s1f, has_bias, bias_n);
-            };
 
             if (!mbar_wait(&tmem_full[b], (it >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
@@ -309,7 +355,10 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                 tmem_ld_wait();
                 if (p.splits == 1) {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) finalize(r[c], m_tile * BT + c0 + c);
+                    for (int c = 0; c < 16; ++c) {
+                        const int m = u.m_tile * BT + c0 + c;
+                        if (n_ok && m < p.M) store_output<kInt8>(p, r[c], m, n, s1f, has_bias, bias_n);
+                    }
                 } else {
 #pragma unroll
                     for (int c = 0; c < 16; ++c) part[(size_t)(c0 + c) * kTileN] = r[c];
@@ -332,8 +381,8 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
             const int j = t + 32 * kExpandGroupWarps * c;
-            // W4: 16-byte chunk j of the [32][128 B] packed tile = weight row 4*(j/8) + (j%8)/2,
-            //     k half j%2 (32 consecutive k).  W8: [128][64 B] int8 tile, row j/2, half j%2.
+            // W4: 16-byte chunk j of a k block's packed [32][128 B] = weight row 4*(j/8) + (j%8)/2,
+            //     k half j%2 (32 consecutive k).  W8: [128][64 B] int8, row j/2, half j%2.
             n_local[c] = kMode == kModeW4 ? 4 * (j >> 3) + ((j & 7) >> 1) : (j >> 1);
             dst_off[c] = (uint32_t)((n_local[c] >> 3) * 1024 + (n_local[c] & 7) * 128);
         }
@@ -341,22 +390,20 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
         uint32_t i = 0;                              // running k-block count of this CTA
         bool ok = true;
         for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
-            const int split = unit % p.splits;
-            const int tile = unit / p.splits;
-            const int n_tile = tile / p.m_tiles;
-            const int kb0 = split * p.kb_per_split;
-            const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+            const UnitRange u = unit_range(p, unit);
             __half2 s8[kChunks];
             if constexpr (kMode == kModeW8) {
 #pragma unroll
                 for (int c = 0; c < kChunks; ++c) {
-                    const int n = n_tile * kTileN + n_local[c];
+                    const int n = u.n_tile * kTileN + n_local[c];
                     s8[c] = __half2half2(n < p.N ? __ldg(p.s1 + n) : __float2half_rn(0.f));
                 }
             }
-            for (int kb = kb0; kb < kb1; ++kb, ++i) {
-                const int s = (int)(i % kStages), as = (int)(i % kAStages);
-                const uint32_t phase = (i / kStages) & 1u, aphase = (i / kAStages) & 1u;
+            for (int kb = u.kb0; kb < u.kb1; ++kb, ++i) {
+                const uint32_t stage_no = i / kSub;
+                const int sub = (int)(i % kSub);
+                const int s = (int)(stage_no % kStages), as = (int)(i % kAStages);
+                const uint32_t phase = (stage_no / kStages) & 1u, aphase = (i / kAStages) & 1u;
                 // Every group observes every stage fill, in order, also those it does not expand: a
                 // parity wait is only valid while the waiter is at most one phase away from the barrier.
                 if (!mbar_wait(&full[s], phase, abort_flag)) { ok = false; break; }
@@ -369,13 +416,16 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                 for (int c = 0; c < kChunks; ++c) {
                     const int j = t + 32 * kExpandGroupWarps * c;
                     if constexpr (kMode == kModeW4) {
-                        raw[c] = *reinterpret_cast<const uint4*>(st + 16 * j);
+                        // packed rows are kSub x 128 bytes long; this k block's 128 bytes start at sub * 128
+                        raw[c] = *reinterpret_cast<const uint4*>(st + (j >> 3) * (kSub * 128) + sub * 128 + (j & 7) * 16);
                         // this row's factors of the k block's group, staged by TMA (zero beyond N)
-                        sc[c] = __half2half2(*reinterpret_cast<const __half*>(st + 4096 + 2 * n_local[c]));
-                        zc[c] = __half2half2(*reinterpret_cast<const __half*>(st + 4096 + 256 + 2 * n_local[c]));
+                        const uint8_t* f = st + Cfg::kPackedBytes + (kSub >= 2 ? (sub >> 1) * 256 : 0) + 2 * n_local[c];
+                        sc[c] = __half2half2(*reinterpret_cast<const __half*>(f));
+                        zc[c] = __half2half2(*reinterpret_cast<const __half*>(f + Cfg::kFactorGroups * 256));
                     } else {
-                        raw[c] = *reinterpret_cast<const uint4*>(st + 32 * j);
-                        raw_hi[c] = *reinterpret_cast<const uint4*>(st + 32 * j + 16);
+                        const uint8_t* src = st + (j >> 1) * (kSub * 64) + sub * 64 + (j & 1) * 32;
+                        raw[c] = *reinterpret_cast<const uint4*>(src);
+                        raw_hi[c] = *reinterpret_cast<const uint4*>(src + 16);
                     }
                 }
                 __syncwarp();
@@ -401,12 +451,12 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                     }
                     uint8_t* dst = a_tile + dst_off[c];
                     const int swz = n_local[c] & 7;
-                    const uint32_t* u = reinterpret_cast<const uint32_t*>(w);
+                    const uint32_t* uw = reinterpret_cast<const uint32_t*>(w);
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
                         const int chunk = (4 * khalf + q4) ^ swz;   // 128-byte swizzle: 16-byte chunk ^ (row % 8)
                         *reinterpret_cast<uint4*>(dst + 16 * chunk) =
-                            make_uint4(u[4 * q4], u[4 * q4 + 1], u[4 * q4 + 2], u[4 * q4 + 3]);
+                            make_uint4(uw[4 * q4], uw[4 * q4 + 1], uw[4 * q4 + 2], uw[4 * q4 + 3]);
                     }
                 }
                 fence_proxy_async_smem();                        // generic-proxy writes -> visible to the MMA
@@ -452,9 +502,9 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// 2-D row-major tensor [rows, cols] of `elem_bytes` elements; box = box_cols x box_rows.
-static int make_tmap(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
-                     uint64_t cols, uint32_t box_cols, uint32_t box_rows, bool swizzle128) {
+// 2-D row-major tensor [rows, cols] of `elem_bytes` elements; box = box_cols x box_rows, no swizzle.
+static int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
+                        uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return note_cuda_error(cudaErrorNotSupported);
     const cuuint64_t dims[2] = {cols, rows};
@@ -462,8 +512,28 @@ static int make_tmap(CUtensorMap* map, const void* base, CUtensorMapDataType dt,
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return note_cuda_error(cudaErrorInvalidValue);
+    return KAIROS_OK;
+}
+
+// Row-major operand [rows, K] seen as k blocks of 128 bytes: dims {128 B of K, rows, K / block};
+// one copy brings `box_kb` consecutive k blocks of `box_rows` rows, each landing as a 128B-swizzled
+// K-major tile [box_rows][128 B] (the layout tcgen05.mma reads), tiles back to back.
+static int make_tmap_kblocks(CUtensorMap* map, const void* base, bool int8, uint64_t rows, uint64_t K,
+                             uint32_t box_rows, uint32_t box_kb) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return note_cuda_error(cudaErrorNotSupported);
+    const uint64_t es = int8 ? 1 : 2, bk = int8 ? 128 : 64;
+    const cuuint64_t dims[3] = {bk, rows, K / bk};
+    const cuuint64_t strides[2] = {K * es, 128};
+    const cuuint32_t box[3] = {(cuuint32_t)bk, box_rows, box_kb};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(map, int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return note_cuda_error(cudaErrorInvalidValue);
     return KAIROS_OK;
 }
@@ -486,6 +556,8 @@ static long long* g_trace = nullptr;   // diagnostic buffer of kTraceBlocks * kT
 
 static int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
+static int stage_bundle(int bt) { return bt <= 64 ? 4 : (bt == 128 ? 2 : 1); }   // GemmCfg::kSub
+
 struct Plan {
     int bt, n_tiles, m_tiles, splits, kb_per_split, kb_total;
     size_t partial_bytes;
@@ -496,18 +568,22 @@ static Plan make_plan(int M, int N, int K, bool int8) {
     pl.bt = token_tile(M);
     pl.n_tiles = (N + kTileN - 1) / kTileN;
     pl.m_tiles = (M + pl.bt - 1) / pl.bt;
-    pl.kb_total = K / (int8 ? 128 : 64);
+    const int sub = stage_bundle(pl.bt);
+    const int stages_total = (K / (int8 ? 128 : 64) + sub - 1) / sub;   // k blocks past K are zero-filled
+    pl.kb_total = stages_total * sub;
     const int tiles = pl.n_tiles * pl.m_tiles;
     const int sms = device_sm_count();
     int splits = 1;
     if (tiles < sms) {
         splits = sms / tiles;
-        const int max_by_k = pl.kb_total / 4 > 0 ? pl.kb_total / 4 : 1;   // at least 4 stages of work per split
+        const int min_stages = 4 / sub;                                   // at least 4 k blocks per split
+        const int max_by_k = stages_total / min_stages > 0 ? stages_total / min_stages : 1;
         if (splits > max_by_k) splits = max_by_k;
         if (splits < 1) splits = 1;
     }
-    pl.kb_per_split = (pl.kb_total + splits - 1) / splits;
-    pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;
+    const int stages_per_split = (stages_total + splits - 1) / splits;
+    pl.splits = (stages_total + stages_per_split - 1) / stages_per_split;
+    pl.kb_per_split = stages_per_split * sub;
     pl.partial_bytes = pl.splits > 1 ? (size_t)tiles * pl.splits * pl.bt * kTileN * 4 : 0;
     return pl;
 }
@@ -537,26 +613,23 @@ static int launch_one(const GemmArgs& a, const Plan& pl) {
     CUtensorMap tw, tx, ts, tz;
     int rc;
     if constexpr (kMode == kModeW4) {
-        rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)a.N / kInterleave, (uint64_t)a.K, 64, 32,
-                       false);
+        rc = make_tmap_2d(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)a.N / kInterleave, (uint64_t)a.K,
+                          64 * Cfg::kSub, 32);
         if (rc != KAIROS_OK) return rc;
-        // factor tensors [K/128 used rows, N] fp16: one 128-wide row slice per (tile, group)
-        rc = make_tmap(&ts, a.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.K / kGroup, (uint64_t)a.N,
-                       kTileN, 1, false);
+        // factor tensors [K/128 used rows, N] fp16: 128-wide row slices, the stage's groups
+        rc = make_tmap_2d(&ts, a.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.K / kGroup, (uint64_t)a.N,
+                          kTileN, Cfg::kFactorGroups);
         if (rc != KAIROS_OK) return rc;
-        rc = make_tmap(&tz, a.scaled_zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.K / kGroup, (uint64_t)a.N,
-                       kTileN, 1, false);
-    } else if constexpr (kMode == kModeW8)
-        rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.N, (uint64_t)a.K, 64, kTileN, false);
-    else if constexpr (kInt8)
-        rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.N, (uint64_t)a.K, 128, kTileN, true);
-    else
-        rc = make_tmap(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.N, (uint64_t)a.K, 64, kTileN, true);
+        rc = make_tmap_2d(&tz, a.scaled_zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.K / kGroup,
+                          (uint64_t)a.N, kTileN, Cfg::kFactorGroups);
+    } else if constexpr (kMode == kModeW8) {
+        rc = make_tmap_2d(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.N, (uint64_t)a.K, 64 * Cfg::kSub,
+                          kTileN);
+    } else {
+        rc = make_tmap_kblocks(&tw, a.W, kInt8, (uint64_t)a.N, (uint64_t)a.K, kTileN, Cfg::kSub);
+    }
     if (rc != KAIROS_OK) return rc;
-    if constexpr (kInt8)
-        rc = make_tmap(&tx, a.X, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)a.M, (uint64_t)a.K, 128, BT, true);
-    else
-        rc = make_tmap(&tx, a.X, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.M, (uint64_t)a.K, 64, BT, true);
+    rc = make_tmap_kblocks(&tx, a.X, kInt8, (uint64_t)a.M, (uint64_t)a.K, BT, Cfg::kSub);
     if (rc != KAIROS_OK) return rc;
     if constexpr (kMode != kModeW4) {
         ts = tx;   // unused by the kernel in these modes

@@ -75,6 +75,18 @@ def gemv_forward_cuda_new(in_feats, kernel, scaling_factors, zeros, m, n, k, gro
     return out
 
 
+def decode_forward(in_feats, kernel, scaling_factors, zeros, m, n, k, bias=None):
+    """W4A16 for 1 <= m <= 16 on the warp-level tensor-core decode kernel."""
+    x = in_feats.reshape(-1, k)
+    out = torch.empty((m, n), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.kairos_w4a16_decode(_chk(x, torch.float16, 'in_feats'), _chk(kernel, torch.int16, 'kernel'),
+                                      _chk(scaling_factors, torch.float16, 'scaling_factors'),
+                                      _chk(zeros, torch.float16, 'zeros'), _bias_ptr(bias), out.data_ptr(), m, n, k,
+                                      stream_ptr()), 'decode_forward')
+    return out
+
+
 def gemm_forward_cuda_new(in_feats, kernel, scaling_factors, zeros, bias=None):
     k = in_feats.shape[-1]
     x = in_feats.reshape(-1, k)

@@ -128,6 +128,26 @@ def test_gemv(kb, m, k, n):
     assert_close(y.cpu().numpy(), ko.y_w4a16(x, res), f'gemv m={m} k={k} n={n}')
 
 
+@pytest.mark.parametrize('m,k,n', [(1, 128, 256), (1, 4096, 4096), (2, 4096, 1024), (3, 1152, 96), (4, 14336, 4096),
+                                   (5, 256, 64), (8, 4096, 14336), (9, 512, 128), (13, 3584, 512),
+                                   (16, 4096, 4096), (16, 18944, 3584)])
+def test_decode_mma(kb, m, k, n):
+    _, ops, _ = kb
+    x, _, res = case(m, k, n, seed=m)
+    r = resident(res)
+    y = ops.decode_forward(dev(x), r['qweight'], r['scales'], r['scaled_zeros'], m, n, k)
+    assert_close(y.cpu().numpy(), ko.y_w4a16(x, res), f'decode m={m} k={k} n={n}')
+
+
+def test_decode_mma_bias_vs_reference_fixture(kb):
+    _, ops, _ = kb
+    g = dict(np.load(os.path.join(GOLDEN, 'small_n96_k1152_m33_bias.npz')))
+    x = g['X'][:11]
+    y = ops.decode_forward(dev(x), dev(g['qweight']), dev(g['scales']), dev(g['scaled_zeros']), 11, 96, 1152,
+                           bias=dev(g['bias']))
+    assert_close(y.cpu().numpy(), g['Y_w4a16'][:11], 'decode + bias vs reference fixture')
+
+
 def test_gemv_bias_and_fixture(kb):
     _, ops, _ = kb
     g = dict(np.load(os.path.join(GOLDEN, 'small_n96_k1152_m33_bias.npz')))
