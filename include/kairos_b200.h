@@ -95,6 +95,11 @@ int kairos_w4a16_gemv(const void* X_f16, const void* qweight, const void* scales
 int kairos_w4a16_decode(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
                         const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, kairos_stream_t stream);
 
+/* Kernel id 1 as the switched linear runs it: picks between the two kernels above by (M, N, K);
+ * 1 <= M <= 32.  This is the drop-in for gemv_forward_cuda_new. */
+int kairos_w4a16_small_batch(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
+                             const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, kairos_stream_t stream);
+
 /* Bytes of scratch the tensor-core GEMMs need for (M,N,K): the split-K partial tiles (0 when
  * the problem is not split; then `workspace` may be null).  Contents need no initialisation.
  * Calls that share a workspace must be ordered (same stream). */

@@ -195,11 +195,7 @@ static int run_switched(Layer* L, const void* X, void* Y, int M, int comp, cudaS
     int rc;
     switch (comp) {
         case KAIROS_COMP_W4A16_GEMV:
-            // two kernels serve this id: the CUDA-core weight streamer wins for a single token on small
-            // matrices, the warp-MMA decode kernel everywhere else up to 16 tokens (measured on B200)
-            if (M <= 16 && !(M == 1 && (size_t)L->N * L->K <= (size_t)4096 * 4096))
-                return kairos_w4a16_decode(X, L->qweight, L->scales, L->scaled_zeros, L->bias, Y, M, L->N, L->K, ks);
-            return kairos_w4a16_gemv(X, L->qweight, L->scales, L->scaled_zeros, L->bias, Y, M, L->N, L->K, ks);
+            return kairos_w4a16_small_batch(X, L->qweight, L->scales, L->scaled_zeros, L->bias, Y, M, L->N, L->K, ks);
         case KAIROS_COMP_W4A16_GEMM:
             if ((rc = ensure_gemm_ws(c, M, L->N, L->K, st)) != KAIROS_OK) return rc;
             return kairos_w4a16_gemm(X, L->qweight, L->scales, L->scaled_zeros, L->bias, Y, M, L->N, L->K, c->gemm_ws,
@@ -268,6 +264,16 @@ int kairos_device_status(int clear) {
     const int v = *reinterpret_cast<volatile int*>(w);
     if (clear) *reinterpret_cast<volatile int*>(w) = 0;
     return v;
+}
+
+/* Kernel id 1 (w4a16_gemv) is served by two kernels: the CUDA-core weight streamer wins for a single
+ * token on small matrices, the warp-MMA decode kernel everywhere else up to 16 tokens (measured on
+ * B200); 17..32 tokens fall back to passes of the CUDA-core kernel. */
+int kairos_w4a16_small_batch(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
+                             const void* bias, void* Y, int M, int N, int K, kairos_stream_t stream) {
+    if (M <= 16 && !(M == 1 && (size_t)N * K <= (size_t)4096 * 4096))
+        return kairos_w4a16_decode(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, stream);
+    return kairos_w4a16_gemv(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, stream);
 }
 
 // ------------------------------- LUT ---------------------------------------

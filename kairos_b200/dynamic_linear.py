@@ -25,6 +25,9 @@ COMP_TYPE_NAME = {'w4a16_gemm': 0, 'w4a16_gemv': 1, 'w8a8': 2,
 COMP_TYPE_ID = {v: k for k, v in COMP_TYPE_NAME.items()}
 SUPPORTED_COMP_TYPES = (0, 1, 2, 3, 5)
 
+_switched_linear = lib.kairos_switched_linear
+_raw_stream = torch._C._cuda_getCurrentRawStream     # current stream of a device index as an integer
+
 _RESIDENT = ('qweight', 'scales', 'scaled_zeros', 'scales_to8', 'scaled_zeros_to8', 'scales_1')
 
 
@@ -133,29 +136,33 @@ class DynamicLinear(torch.nn.Module):
         except Exception:
             pass
 
+    def _apply(self, fn, *args, **kwargs):
+        # .to() / .cuda() / .half() may move the buffers: the native handle holds raw pointers
+        self._release()
+        return super()._apply(fn, *args, **kwargs)
+
     # ---- forward ----------------------------------------------------------
     @torch.no_grad()
     def forward(self, input: torch.Tensor) -> torch.Tensor:
         shape = input.shape
-        input = input.reshape(-1, shape[-1])
-        m = input.shape[-2]
+        m = input.numel() // shape[-1]
         if m != self.pre_m:
             self.pre_m = m
             self.comp_type = type(self).prof.get_comp_type(self.shape, m)
-        return self._forward(input, m, self.comp_type).reshape(shape[0], shape[1], -1)
+        return self._forward(input, m, self.comp_type).view(shape[0], shape[1], -1)
 
     @torch.no_grad()
     def _forward(self, input: torch.Tensor, batch_token_len, comp_type) -> torch.Tensor:
         """Run kernel `comp_type` on input [M, K] (or [..., K]) and return [M, N]."""
-        x = input.reshape(-1, self.in_features)
+        x = input if input.dim() == 2 else input.reshape(-1, self.in_features)
         if x.dtype != torch.float16:
             x = x.to(torch.float16)
         if not x.is_contiguous():
             x = x.contiguous()
         m = x.shape[0]
         out = torch.empty((m, self.out_features), dtype=torch.float16, device=x.device)
-        rc = lib.kairos_switched_linear(self._native(), x.data_ptr(), out.data_ptr(), m, int(comp_type),
-                                        torch.cuda.current_stream(x.device).cuda_stream)
+        rc = _switched_linear(self._handle or self._native(), x.data_ptr(), out.data_ptr(), m, comp_type,
+                              _raw_stream(x.device.index))
         if rc:
             check(rc, f'DynamicLinear._forward(comp_type={comp_type}, m={m}, shape={self.shape})')
         return out

@@ -64,7 +64,20 @@ def _bias_ptr(bias):
 
 
 def gemv_forward_cuda_new(in_feats, kernel, scaling_factors, zeros, m, n, k, group_size=128, bias=None):
+    """Kernel id 1 as the switched linear runs it (CUDA-core streamer or warp-MMA decode kernel)."""
     assert group_size == 128
+    x = in_feats.reshape(-1, k)
+    out = torch.empty((m, n), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.kairos_w4a16_small_batch(_chk(x, torch.float16, 'in_feats'), _chk(kernel, torch.int16, 'kernel'),
+                                           _chk(scaling_factors, torch.float16, 'scaling_factors'),
+                                           _chk(zeros, torch.float16, 'zeros'), _bias_ptr(bias), out.data_ptr(), m,
+                                           n, k, stream_ptr()), 'gemv_forward_cuda_new')
+    return out
+
+
+def gemv_cuda_core(in_feats, kernel, scaling_factors, zeros, m, n, k, bias=None):
+    """The CUDA-core weight-streaming GEMV alone, 1 <= m <= 32."""
     x = in_feats.reshape(-1, k)
     out = torch.empty((m, n), dtype=torch.float16, device=x.device)
     with torch.cuda.device(x.device):

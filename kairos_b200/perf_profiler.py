@@ -137,20 +137,16 @@ def collapse_segments(perf_list):
 
 
 @torch.no_grad()
-def time_forward(layer, x, m, comp_id, n, warmup, cold):
-    """Mean milliseconds of one ``_forward`` over n back-to-back calls (CUDA events)."""
-    ctx = layer._cache_context() if layer._handle is None else layer._ctx
+def time_forward(layer, x, m, comp_id, n, warmup):
+    """Mean milliseconds of one ``_forward`` over n back-to-back calls (CUDA events,
+    utils/perf_eval.py:21-34 of the reference)."""
     for _ in range(warmup):
-        if cold:
-            ctx.clear_cache()
         layer._forward(x, m, comp_id)
     torch.cuda.synchronize()
     start = torch.cuda.Event(enable_timing=True)
     end = torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(n):
-        if cold:
-            ctx.clear_cache()
         layer._forward(x, m, comp_id)
     end.record()
     torch.cuda.synchronize()
@@ -167,13 +163,12 @@ def test_perf(proj_name, K, N, bias, m_grid=None, candidates=None, n=200, warmup
     lin = torch.nn.Linear(K, N, bias=bias, dtype=torch.float16, device=device)
     layer = linear_cls.from_module(lin, device)
     del lin
-    cold = cache == 'cold'
-    if cold:
-        # a zero-byte cache converts into one reusable slot on every call (no allocator traffic)
-        from .runtime import Context
-        layer._release()
-        cold_ctx = Context(layer.qweight.device, cache_bytes=0)
-        layer._cache_context = lambda: cold_ctx
+    from .runtime import Context
+    layer._release()
+    # cold: a zero-byte cache converts into one reusable slot on every call (no allocator traffic);
+    # warm: a private unbounded cache keeps the converted weight after the first call
+    own_ctx = Context(layer.qweight.device, cache_bytes=0 if cache == 'cold' else None)
+    layer._cache_context = lambda: own_ctx
     table, perf_list = {}, []
     for m in m_grid:
         x = torch.randn((m, K), dtype=torch.float16, device=device)
@@ -182,7 +177,7 @@ def test_perf(proj_name, K, N, bias, m_grid=None, candidates=None, n=200, warmup
         for name in candidates:
             if m > 32 and 'gemv' in name:
                 continue
-            t = time_forward(layer, x, m, COMP_TYPE_NAME[name], n, warmup, False)
+            t = time_forward(layer, x, m, COMP_TYPE_NAME[name], n, warmup)
             table[m][name] = t
             if t < best_t:
                 best_t, best = t, name

@@ -124,8 +124,10 @@ def test_gemv(kb, m, k, n):
     _, ops, _ = kb
     x, _, res = case(m, k, n, seed=m)
     r = resident(res)
-    y = ops.gemv_forward_cuda_new(dev(x), r['qweight'], r['scales'], r['scaled_zeros'], m, n, k, 128)
+    y = ops.gemv_cuda_core(dev(x), r['qweight'], r['scales'], r['scaled_zeros'], m, n, k)
     assert_close(y.cpu().numpy(), ko.y_w4a16(x, res), f'gemv m={m} k={k} n={n}')
+    y = ops.gemv_forward_cuda_new(dev(x), r['qweight'], r['scales'], r['scaled_zeros'], m, n, k, 128)
+    assert_close(y.cpu().numpy(), ko.y_w4a16(x, res), f'small-batch entry m={m} k={k} n={n}')
 
 
 @pytest.mark.parametrize('m,k,n', [(1, 128, 256), (1, 4096, 4096), (2, 4096, 1024), (3, 1152, 96), (4, 14336, 4096),
@@ -152,8 +154,8 @@ def test_gemv_bias_and_fixture(kb):
     _, ops, _ = kb
     g = dict(np.load(os.path.join(GOLDEN, 'small_n96_k1152_m33_bias.npz')))
     x = g['X'][:7]
-    y = ops.gemv_forward_cuda_new(dev(x), dev(g['qweight']), dev(g['scales']), dev(g['scaled_zeros']), 7, 96, 1152,
-                                  128, bias=dev(g['bias']))
+    y = ops.gemv_cuda_core(dev(x), dev(g['qweight']), dev(g['scales']), dev(g['scaled_zeros']), 7, 96, 1152,
+                           bias=dev(g['bias']))
     assert_close(y.cpu().numpy(), g['Y_w4a16'][:7], 'gemv + bias vs reference fixture')
 
 
