@@ -440,6 +440,8 @@ def run_gpu_arm(args):
         'clocks': clocks,
         'lut': {str(s): prof.seg_perf_list[i] for i, s in enumerate(shapes)},
         'lut_cold': {str(s): prof_cold.seg_perf_list[i] for i, s in enumerate(shapes)},
+        'profile_us': {str(s): {str(m): {k2: round(v * 1e3, 2) for k2, v in row.items()}
+                                for m, row in prof.timings[s].items()} for s in shapes},
         'peaks': peaks,
     }
     if roof:

@@ -266,12 +266,11 @@ int kairos_device_status(int clear) {
     return v;
 }
 
-/* Kernel id 1 (w4a16_gemv) is served by two kernels: the CUDA-core weight streamer wins for a single
- * token on small matrices, the warp-MMA decode kernel everywhere else up to 16 tokens (measured on
- * B200); 17..32 tokens fall back to passes of the CUDA-core kernel. */
+/* Kernel id 1 (w4a16_gemv) is served by two kernels: the TMA-pipelined warp-MMA decode kernel up to
+ * 16 tokens (N % 8 == 0), passes of the CUDA-core weight streamer otherwise (17..32 tokens, odd N). */
 int kairos_w4a16_small_batch(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
                              const void* bias, void* Y, int M, int N, int K, kairos_stream_t stream) {
-    if (M <= 16 && !(M == 1 && (size_t)N * K <= (size_t)4096 * 4096))
+    if (M <= 16 && (N % 8) == 0)
         return kairos_w4a16_decode(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, stream);
     return kairos_w4a16_gemv(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, stream);
 }

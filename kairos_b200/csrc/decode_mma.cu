@@ -1,34 +1,66 @@
-// Decode-side W4A16 for small batches on the legacy warp-level tensor path (path item a9,
-// batches the CUDA-core GEMV cannot serve at HBM speed): Y[M,N] = X[M,K] . dequant(W)^T, M <= 16.
+// Decode-side W4A16 for small batches (path item a9): Y[M,N] = X[M,K] . dequant(W)^T, 1 <= M <= 16.
 //
-// Weight streaming is the only large traffic, so the kernel is built around the packed base:
-//   * a warp step is one quantization group (128 k) of 64 weight rows = 4 KB of qweight, read as
-//     eight 128-bit loads per lane that coalesce into full 128-byte lines;
-//   * the uint4 values never leave registers: one lop3 turns a nibble pair into the fp16 pair
-//     (1024 + q) -- or (1024 + 16 q) for the odd nibbles -- which goes straight into the A
-//     fragment of mma.sync.m16n8k16 (fp32 accumulate).  No subtraction, no scaling per element;
+// Weight streaming is the only large traffic, so the kernel is a persistent TMA pipeline around
+// the packed base with the arithmetic kept off the critical path:
+//   * one CTA per SM walks 32-row units of the weight over the full K.  Two producer warps bring
+//     1024-k panels into a shared-memory ring with bulk tensor copies -- 16 KB of qweight, the panel's
+//     activations and its (scale, scaled-zero) tiles per stage -- several stages ahead of use, so the
+//     bytes in flight do not depend on registers or occupancy;
+//   * consumer warps each own one of a panel's eight quantization groups (both 16-row blocks of the
+//     unit, so a lane's activations are read once); for M <= 8 two sets of eight warps take alternate
+//     panels.  The uint4 values go from shared memory through ONE lop3 per pair into the A
+//     fragment of mma.sync.m16n8k16 as fp16 (1024 + q) -- or (1024 + 16 q) for the odd nibbles --
+//     with fp32 accumulation: no subtraction, no scaling per element;
 //   * the offsets are undone per group on the accumulators:  sum q x = (C_lo - 1024 X_lo)
-//     + (C_hi - 1024 X_hi) / 16, where X_lo / X_hi = sum of x over the k of even / odd nibbles come
-//     from one extra MMA against an all-ones A fragment; then y += s * (sum q x) + z * (X_lo + X_hi)
+//     + (C_hi - 1024 X_hi) / 16, where X_lo / X_hi (sums of x over the k of the even / odd nibbles)
+//     come from MMAs against an all-ones A fragment; then y += s * (sum q x) + z * (X_lo + X_hi)
 //     with the stored per-group fp16 factors, in fp32;
-//   * every lane's 32 k of activations (64 bytes per token) are loaded once per step and reused by
-//     the four 16-row blocks of the step.
-// K is split over the 8 warps of a CTA (shared-memory reduction) and, for shapes with few row
-// blocks, over the CTAs of a thread-block cluster (reduction through distributed shared memory).
-// No scratch memory, no atomics, one launch.
+//   * the K slices of a unit (one per consumer warp) meet in shared memory at its end.
+// No scratch memory, no atomics, one launch.  Every wait is bounded (status word on timeout).
 //
 // Algorithmic bytes per call: K*N/2 + 4*(K/128)*N + 2*M*K + 2*M*N.
-#include <cooperative_groups.h>
+#include <cuda.h>
 
 #include "common.cuh"
 
-namespace cg = cooperative_groups;
-
 namespace kairos {
 
-constexpr int kDecThreads = 256;
-constexpr int kDecWarps = kDecThreads / 32;
-constexpr int kDecRows = 64;              // weight rows per CTA (4 blocks of 16)
+int make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle);   // tensormap.cu
+int device_sm_count();        // gemm_sm100.cu
+int* device_status_word();    // api.cu
+
+constexpr int kDecRows = 32;                 // weight rows per unit (two MMA row blocks)
+constexpr int kDecPanelK = 1024;             // k per pipeline stage (eight groups)
+constexpr int kDecGroups = kDecPanelK / kGroup;
+constexpr int kDecSetWarps = 8;              // consumer warps per set: one per quantization group of a panel
+constexpr int kDecWBytes = (kDecRows / kInterleave) * kDecPanelK * 2;   // 16 KB: [8 qweight rows][2048 B]
+constexpr int kDecFBytes = kDecGroups * kDecRows * 2;                    // 512 B: [8 groups][32 rows] fp16
+
+template <int NT>
+struct DecCfg {
+    static constexpr int kXRows = 8 * NT;
+    static constexpr int kXBytes = kXRows * kDecPanelK * 2;              // [tokens][32 chunks][64 B], 64B-swizzled
+    static constexpr int kStageBytes = kDecWBytes + kXBytes + 2 * kDecFBytes;
+    static constexpr int kStages = NT == 1 ? 5 : 3;
+    // consumer sets take alternate panels: more warps per scheduler hide the unpack -> MMA -> scale chain
+    static constexpr int kSets = NT == 1 ? 2 : 1;
+    static constexpr int kConsumers = kSets * kDecSetWarps;
+    static constexpr int kThreads = 32 * (kConsumers + 2);               // + weight and activation producers
+    static constexpr int kRedFloats = kConsumers * kDecRows * 8 * NT;    // per-warp partials of one unit
+    static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kRedFloats * 4 + 8 * (2 * kStages + 2) + 64 + 1024;
+    static_assert(kSmemBytes <= 227 * 1024, "exceeds the shared memory a CTA may use");
+    static_assert(kStageBytes % 1024 == 0, "stages must keep the swizzle alignment");
+};
+
+struct DecParams {
+    const __half* bias;
+    __half* Y;
+    int M, N, K;
+    int units;      // 32-row units
+    int panels;     // 1024-k panels per unit
+    int* status;
+};
 
 __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                              uint32_t b0, uint32_t b1) {
@@ -48,217 +80,288 @@ __device__ __forceinline__ void nibble_pairs(uint32_t w, uint32_t (&e)[4]) {
 }
 
 template <int NT>   // token tiles of 8: 1 (M <= 8) or 2 (M <= 16)
-__global__ void __launch_bounds__(kDecThreads, 2) decode_mma_kernel(const __half* __restrict__ X,
-                                                                 const uint4* __restrict__ qweight,
-                                                                 const __half* __restrict__ scales,
-                                                                 const __half* __restrict__ scaled_zeros,
-                                                                 const __half* __restrict__ bias,
-                                                                 __half* __restrict__ Y, int M, int N, int K,
-                                                                 int ksplit) {
-    __shared__ float red[kDecWarps][kDecRows][8 * NT];        // per-warp partial outputs
+__global__ void __launch_bounds__(DecCfg<NT>::kThreads, 1)
+    decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                      const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_z,
+                      const DecParams p) {
+    using Cfg = DecCfg<NT>;
+    constexpr int kStages = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* stage_base = smem;
+    float* red = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);
+    uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * Cfg::kRedFloats);
+    uint64_t* empty = full + kStages;
+    uint64_t* unit_bar = empty + kStages;          // [2]: the partial sums of a unit are in `red`
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(unit_bar + 2);
+
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int row_base = (blockIdx.x / ksplit) * kDecRows;
-    const int krank = blockIdx.x % ksplit;                    // this CTA's slice of K (= rank in the cluster)
-    const int groups = K / kGroup;
-    const int groups_per_cta = (groups + ksplit - 1) / ksplit;
-    const int grp_begin = krank * groups_per_cta;
-    const int grp_end = min(groups, grp_begin + groups_per_cta);
-
-    float acc[4][NT][4];
-#pragma unroll
-    for (int rb = 0; rb < 4; ++rb)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[rb][nt][i] = 0.f;
-
-    // rows of this lane: block rb -> rows row_base + 16 rb + g and + 8
-    int chunk_off[4][2];       // 16-byte index of (row, k = 0) minus the k part
-    bool row_ok[4][2];
-#pragma unroll
-    for (int rb = 0; rb < 4; ++rb)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int row = row_base + 16 * rb + g + 8 * h;
-            row_ok[rb][h] = row < N;
-            chunk_off[rb][h] = (row >> 2) * (K / 8) + 2 * (row & 3);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 2);                       // the two producers
+            mbar_init(&empty[s], kDecSetWarps);            // the set that consumed the panel
         }
-    const uint32_t ones = 0x3c003c00u;     // half2(1, 1)
+        mbar_init(&unit_bar[0], Cfg::kConsumers);
+        mbar_init(&unit_bar[1], Cfg::kConsumers);
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_x);
+        tma_prefetch_desc(&tmap_s);
+        tma_prefetch_desc(&tmap_z);
+    }
+    __syncthreads();
 
-    for (int grp = grp_begin + warp; grp < grp_end; grp += kDecWarps) {
-        // lane's 32 k of this group: k block 2*grp + (t >> 1), half t & 1
-        const int kc = 8 * (2 * grp + (t >> 1)) + (t & 1);              // 16-byte chunk column
-        uint4 raw[4][2];
-#pragma unroll
-        for (int rb = 0; rb < 4; ++rb)
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-                raw[rb][h] = row_ok[rb][h] ? __ldg(qweight + chunk_off[rb][h] + kc) : make_uint4(0, 0, 0, 0);
-        // activations of token g (and g + 8): the same 32 k, 64 bytes
-        uint4 xv[NT][4];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const int tok = g + 8 * nt;
-            const uint4* xp = reinterpret_cast<const uint4*>(X + (size_t)min(tok, M - 1) * K + kGroup * grp + 32 * t);
-#pragma unroll
-            for (int b = 0; b < 4; ++b) xv[nt][b] = tok < M ? __ldg(xp + b) : make_uint4(0, 0, 0, 0);
+    if (warp == Cfg::kConsumers) {
+        // ---------------- producer: packed weights + scales ----------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; unit < p.units && ok; unit += gridDim.x) {
+                for (int pn = 0; pn < p.panels; ++pn) {
+                    if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* st = stage_base + s * Cfg::kStageBytes;
+                    mbar_arrive_expect_tx(&full[s], kDecWBytes + kDecFBytes);
+                    // qweight [N/4][k blocks][128 B]: 16 k blocks (1024 k) of 8 rows
+                    tma_load_3d(st, &tmap_w, &full[s], 0, pn * (kDecPanelK / 64), unit * (kDecRows / kInterleave));
+                    tma_load_2d(st + kDecWBytes + Cfg::kXBytes, &tmap_s, &full[s], unit * kDecRows, pn * kDecGroups);
+                    if (++s == kStages) { s = 0; phase ^= 1; }
+                }
+            }
         }
-        __half sc[4][2], zc[4][2];
+    } else if (warp == Cfg::kConsumers + 1) {
+        // ---------------- producer: activations + scaled zeros ----------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; unit < p.units && ok; unit += gridDim.x) {
+                for (int pn = 0; pn < p.panels; ++pn) {
+                    if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* st = stage_base + s * Cfg::kStageBytes;
+                    mbar_arrive_expect_tx(&full[s], Cfg::kXBytes + kDecFBytes);
+                    // X as [M][K/32][32 halves]: 32 chunks of 64 bytes for every token row
+                    tma_load_3d(st + kDecWBytes, &tmap_x, &full[s], 0, pn * 32, 0);
+                    tma_load_2d(st + kDecWBytes + Cfg::kXBytes + kDecFBytes, &tmap_z, &full[s], unit * kDecRows,
+                                pn * kDecGroups);
+                    if (++s == kStages) { s = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else {
+        // ---------------- consumers ----------------
+        // warp w owns quantization group w % 8 of the panels of its set, for both 16-row blocks of the unit
+        const int g = lane >> 2, t = lane & 3;
+        const int grp = warp % kDecSetWarps;
+        const int set = warp / kDecSetWarps;
+        const uint32_t ones = 0x3c003c00u;           // half2(1, 1)
+        // packed chunk of (row r, this group): qweight row r >> 2, k block k0 = 2 grp + (t >> 1), 16-byte
+        // unit 2 (r & 3) + (t & 1) of its 128-byte line, XOR-swizzled by k0 & 7 (128-byte swizzle)
+        const int k0 = 2 * grp + (t >> 1);
+        uint32_t w_off[2][2];
 #pragma unroll
-        for (int rb = 0; rb < 4; ++rb)
+        for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const int row = row_base + 16 * rb + g + 8 * h;
-                sc[rb][h] = row_ok[rb][h] ? __ldg(scales + (size_t)grp * N + row) : __float2half_rn(0.f);
-                zc[rb][h] = row_ok[rb][h] ? __ldg(scaled_zeros + (size_t)grp * N + row) : __float2half_rn(0.f);
+                const int r = 16 * rb + g + 8 * h;
+                w_off[rb][h] = (uint32_t)((r >> 2) * (kDecPanelK * 2) + k0 * 128 +
+                                          (((2 * (r & 3) + (t & 1)) ^ (k0 & 7)) << 4));
             }
-
-        // X_lo / X_hi of tokens (2t, 2t+1): ones . x over the k of even / odd nibbles
-        float xs_lo[NT][4], xs_hi[NT][4];
+        // activations of token g (+ 8 nt): chunk 4 grp + t (64 bytes); the 16-byte units are XOR-swizzled by
+        // bits 7-8 of the offset (64-byte swizzle)
+        uint32_t x_off[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t base = (uint32_t)((g + 8 * nt) * (kDecPanelK * 2) + (4 * grp + t) * 64);
+            const uint32_t sw = (base >> 7) & 3u;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) xs_lo[nt][i] = xs_hi[nt][i] = 0.f;
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv[nt][b]);
-                if (b & 1) {
-                    mma_m16n8k16(xs_hi[nt], ones, ones, ones, ones, xw[0], xw[1]);
-                    mma_m16n8k16(xs_hi[nt], ones, ones, ones, ones, xw[2], xw[3]);
-                } else {
-                    mma_m16n8k16(xs_lo[nt], ones, ones, ones, ones, xw[0], xw[1]);
-                    mma_m16n8k16(xs_lo[nt], ones, ones, ones, ones, xw[2], xw[3]);
-                }
-            }
+            for (int b = 0; b < 4; ++b) x_off[nt][b] = kDecWBytes + base + ((b ^ sw) << 4);
         }
+        int s = 0, it = 0;
+        uint32_t phase = 0, panel_no = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; unit < p.units && ok; unit += gridDim.x, ++it) {
+            float acc[2][NT][4];
+#pragma unroll
+            for (int rb = 0; rb < 2; ++rb)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[rb][nt][i] = 0.f;
 
-#pragma unroll
-        for (int rb = 0; rb < 4; ++rb) {
-            float c_lo[NT][4], c_hi[NT][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) c_lo[nt][i] = c_hi[nt][i] = 0.f;
-            // e0[c][b], e1[c][b]: nibble pairs of the chunk of row g / row g + 8
-            uint32_t e0[4][4], e1[4][4];
-            nibble_pairs(raw[rb][0].x, e0[0]); nibble_pairs(raw[rb][0].y, e0[1]);
-            nibble_pairs(raw[rb][0].z, e0[2]); nibble_pairs(raw[rb][0].w, e0[3]);
-            nibble_pairs(raw[rb][1].x, e1[0]); nibble_pairs(raw[rb][1].y, e1[1]);
-            nibble_pairs(raw[rb][1].z, e1[2]); nibble_pairs(raw[rb][1].w, e1[3]);
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                // k = 8b + 2c (+d): the four pairs c = 0..3 of nibble b line up with the b-th 16 bytes of x
+            for (int pn = 0; pn < p.panels && ok; ++pn) {
+                // every warp observes every stage fill in order (a parity wait is only valid one phase
+                // away from the barrier); the other set's panels are skipped after the wait
+                if (!mbar_wait(&full[s], phase, abort_flag)) { ok = false; break; }
+                const uint8_t* st = stage_base + s * Cfg::kStageBytes;
+                const int s_now = s;
+                if (++s == kStages) { s = 0; phase ^= 1; }
+                if (Cfg::kSets > 1 && ((panel_no++ % Cfg::kSets) != (uint32_t)set)) continue;
+                // activations (only the lanes whose token exists touch shared memory) and their sums over
+                // the k of the even / odd nibbles, by MMAs against an all-ones A fragment
+                uint4 xv[NT][4];
+                float x_lo[NT][4], x_hi[NT][4];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv[nt][b]);
-                    if (b & 1) {
-                        mma_m16n8k16(c_hi[nt], e0[0][b], e1[0][b], e0[1][b], e1[1][b], xw[0], xw[1]);
-                        mma_m16n8k16(c_hi[nt], e0[2][b], e1[2][b], e0[3][b], e1[3][b], xw[2], xw[3]);
-                    } else {
-                        mma_m16n8k16(c_lo[nt], e0[0][b], e1[0][b], e0[1][b], e1[1][b], xw[0], xw[1]);
-                        mma_m16n8k16(c_lo[nt], e0[2][b], e1[2][b], e0[3][b], e1[3][b], xw[2], xw[3]);
+                    const bool tok_ok = g + 8 * nt < p.M;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b)
+                        xv[nt][b] = tok_ok ? *reinterpret_cast<const uint4*>(st + x_off[nt][b]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) x_lo[nt][i] = x_hi[nt][i] = 0.f;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv[nt][b]);
+                        if (b & 1) {
+                            mma_m16n8k16(x_hi[nt], ones, ones, ones, ones, xw[0], xw[1]);
+                            mma_m16n8k16(x_hi[nt], ones, ones, ones, ones, xw[2], xw[3]);
+                        } else {
+                            mma_m16n8k16(x_lo[nt], ones, ones, ones, ones, xw[0], xw[1]);
+                            mma_m16n8k16(x_lo[nt], ones, ones, ones, ones, xw[2], xw[3]);
+                        }
+                    }
+                    // tokens 2t, 2t+1: x_sum = X_lo + X_hi and the offset 1024 (X_lo + X_hi / 16) to remove
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const float xl = x_lo[nt][j], xh = x_hi[nt][j];
+                        x_lo[nt][j] = xl + xh;                        // reused as x_sum
+                        x_hi[nt][j] = 1024.f * xl + 64.f * xh;        // reused as the offset
                     }
                 }
-            }
-            // c[0], c[1]: row g, tokens 2t, 2t+1;  c[2], c[3]: row g + 8, same tokens
+                const __half* fs = reinterpret_cast<const __half*>(st + kDecWBytes + Cfg::kXBytes) + grp * kDecRows;
+                const __half* fz = fs + kDecGroups * kDecRows;
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
+                for (int rb = 0; rb < 2; ++rb) {
+                    const uint4 raw0 = *reinterpret_cast<const uint4*>(st + w_off[rb][0]);
+                    const uint4 raw1 = *reinterpret_cast<const uint4*>(st + w_off[rb][1]);
+                    const float sc0 = __half2float(fs[16 * rb + g]), sc1 = __half2float(fs[16 * rb + g + 8]);
+                    const float zc0 = __half2float(fz[16 * rb + g]), zc1 = __half2float(fz[16 * rb + g + 8]);
+                    uint32_t e0[4][4], e1[4][4];          // [c][b] nibble pairs of row g / row g + 8
+                    nibble_pairs(raw0.x, e0[0]); nibble_pairs(raw0.y, e0[1]);
+                    nibble_pairs(raw0.z, e0[2]); nibble_pairs(raw0.w, e0[3]);
+                    nibble_pairs(raw1.x, e1[0]); nibble_pairs(raw1.y, e1[1]);
+                    nibble_pairs(raw1.z, e1[2]); nibble_pairs(raw1.w, e1[3]);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int h = i >> 1;
-                    const float xl = xs_lo[nt][i & 1], xh = xs_hi[nt][i & 1];
-                    const float qx = (c_lo[nt][i] - 1024.f * xl) + (c_hi[nt][i] - 1024.f * xh) * 0.0625f;
-                    acc[rb][nt][i] += __half2float(sc[rb][h]) * qx + __half2float(zc[rb][h]) * (xl + xh);
+                    for (int nt = 0; nt < NT; ++nt) {
+                        float c_lo[4] = {0.f, 0.f, 0.f, 0.f}, c_hi[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            // k = 8b + 2c (+d): the pairs c = 0..3 of nibble b line up with the b-th 16 bytes of x
+                            const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv[nt][b]);
+                            if (b & 1) {
+                                mma_m16n8k16(c_hi, e0[0][b], e1[0][b], e0[1][b], e1[1][b], xw[0], xw[1]);
+                                mma_m16n8k16(c_hi, e0[2][b], e1[2][b], e0[3][b], e1[3][b], xw[2], xw[3]);
+                            } else {
+                                mma_m16n8k16(c_lo, e0[0][b], e1[0][b], e0[1][b], e1[1][b], xw[0], xw[1]);
+                                mma_m16n8k16(c_lo, e0[2][b], e1[2][b], e0[3][b], e1[3][b], xw[2], xw[3]);
+                            }
+                        }
+                        // c[0], c[1]: row g, tokens 2t, 2t+1;  c[2], c[3]: row g + 8, same tokens
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float qx = fmaf(c_hi[i], 0.0625f, c_lo[i]) - x_hi[nt][i & 1];
+                            acc[rb][nt][i] = fmaf(i < 2 ? sc0 : sc1, qx, acc[rb][nt][i]);
+                            acc[rb][nt][i] = fmaf(i < 2 ? zc0 : zc1, x_lo[nt][i & 1], acc[rb][nt][i]);
+                        }
+                    }
                 }
-        }
-    }
-
-    // ---- reduce over the warps of the CTA ----
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s_now]);
+            }
+            if (!ok) break;
+            // ---- the K slices (one per warp) meet in shared memory ----
+            float* buf = red + (it & 1) * Cfg::kRedFloats;
+            float* slab = buf + warp * (kDecRows * 8 * NT);
 #pragma unroll
-    for (int rb = 0; rb < 4; ++rb)
+            for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+                for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                red[warp][16 * rb + g + 8 * (i >> 1)][8 * nt + 2 * t + (i & 1)] = acc[rb][nt][i];
-    __syncthreads();
-    float* out = &red[0][0][0];                // [row][token] sums of this CTA, in place of warp 0's slab
-    for (int o = threadIdx.x; o < kDecRows * 8 * NT; o += kDecThreads) {
-        float v = 0.f;
+                    for (int i = 0; i < 4; ++i)
+                        slab[(16 * rb + g + 8 * (i >> 1)) * (8 * NT) + 8 * nt + 2 * t + (i & 1)] = acc[rb][nt][i];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&unit_bar[it & 1]);
+            if (!mbar_wait(&unit_bar[it & 1], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+            // 32 rows x 8 NT tokens, one output per thread (consecutive threads -> consecutive rows)
+            for (int o = threadIdx.x; o < kDecRows * 8 * NT; o += 32 * Cfg::kConsumers) {
+                const int tok = o / kDecRows, r = o % kDecRows;
+                const int n = unit * kDecRows + r;
+                if (tok >= p.M || n >= p.N) continue;
+                float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < kDecWarps; ++w) v += (&red[w][0][0])[o];
-        __syncwarp();
-        out[o] = v;                            // o is owned by this thread in every slab: no hazard
-    }
-    // ---- reduce over the CTAs of the cluster (K slices), rank 0 writes ----
-    if (ksplit > 1) {
-        cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();
-        if (krank == 0) {
-            for (int o = threadIdx.x; o < kDecRows * 8 * NT; o += kDecThreads) {
-                float v = out[o];
-                for (int r = 1; r < ksplit; ++r) v += cluster.map_shared_rank(out, r)[o];
-                out[o] = v;
+                for (int sl = 0; sl < Cfg::kConsumers; ++sl) v += buf[sl * (kDecRows * 8 * NT) + r * (8 * NT) + tok];
+                __half y = __float2half_rn(v);
+                if (p.bias) y = __hadd(y, p.bias[n]);
+                p.Y[(size_t)tok * p.N + n] = y;
             }
         }
-        cluster.sync();                        // remote shared memory stays valid until it has been read
-        if (krank != 0) return;
     }
     __syncthreads();
-    // token-major write: consecutive threads -> consecutive rows
-    for (int o = threadIdx.x; o < kDecRows * 8 * NT; o += kDecThreads) {
-        const int tok = o / kDecRows, r = o % kDecRows;
-        const int n = row_base + r;
-        if (tok >= M || n >= N) continue;
-        __half y = __float2half_rn(out[r * (8 * NT) + tok]);
-        if (bias) y = __hadd(y, bias[n]);
-        Y[(size_t)tok * N + n] = y;
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, KAIROS_ERR_DEVICE);
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);    // let issued copies land before the CTA leaves
     }
 }
 
-int device_sm_count();   // gemm_sm100.cu
+template <int NT>
+static int launch_decode(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
+                         const void* bias, void* Y, int M, int N, int K, cudaStream_t stream) {
+    using Cfg = DecCfg<NT>;
+    CUtensorMap tw, tx, ts, tz;
+    int rc;
+    {   // qweight int16 [N/4, K] viewed as [N/4][K/64 k blocks][64]: 128-byte lines, 128-byte swizzle
+        const uint64_t dims[3] = {64, (uint64_t)K / 64, (uint64_t)N / 4}, strides[2] = {128, (uint64_t)K * 2};
+        const uint32_t box[3] = {64, kDecPanelK / 64, kDecRows / kInterleave};
+        if ((rc = make_tmap(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, qweight, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B)) != KAIROS_OK) return rc;
+    }
+    {   // X fp16 [M, K] viewed as [M][K/32][32]
+        const uint64_t dims[3] = {32, (uint64_t)K / 32, (uint64_t)M}, strides[2] = {64, (uint64_t)K * 2};
+        const uint32_t box[3] = {32, 32, (uint32_t)Cfg::kXRows};
+        if ((rc = make_tmap(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, X, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_64B)) != KAIROS_OK) return rc;
+    }
+    {   // factors fp16 [K/128, N]
+        const uint64_t dims[2] = {(uint64_t)N, (uint64_t)K / kGroup}, strides[1] = {(uint64_t)N * 2};
+        const uint32_t box[2] = {kDecRows, kDecGroups};
+        if ((rc = make_tmap(&ts, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, scales, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_NONE)) != KAIROS_OK) return rc;
+        if ((rc = make_tmap(&tz, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, scaled_zeros, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_NONE)) != KAIROS_OK) return rc;
+    }
+    DecParams p;
+    p.bias = static_cast<const __half*>(bias);
+    p.Y = static_cast<__half*>(Y);
+    p.M = M; p.N = N; p.K = K;
+    p.units = (N + kDecRows - 1) / kDecRows;
+    p.panels = (K + kDecPanelK - 1) / kDecPanelK;
+    p.status = device_status_word();
+    if (!p.status) return KAIROS_ERR_CUDA;
+    static bool attr_set = false;
+    if (!attr_set) {
+        KAIROS_CUDA_OK(cudaFuncSetAttribute(decode_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            Cfg::kSmemBytes));
+        attr_set = true;
+    }
+    const int sms = device_sm_count();
+    const int grid = p.units < sms ? p.units : sms;
+    decode_mma_kernel<NT><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tw, tx, ts, tz, p);
+    return launch_status();
+}
 
 }  // namespace kairos
 
-/* Decode-side W4A16 on warp-level tensor-core instructions, 1 <= M <= 16. */
+/* Decode-side W4A16 on warp-level tensor-core instructions, 1 <= M <= 16 (N % 8 == 0). */
 extern "C" int kairos_w4a16_decode(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
                                    const void* bias, void* Y, int M, int N, int K, kairos_stream_t stream) {
     using namespace kairos;
-    if (M < 0 || M > 16 || N <= 0 || K <= 0 || (N % kInterleave) != 0 || (K % kGroup) != 0) return KAIROS_ERR_SHAPE;
+    if (M < 0 || M > 16 || N <= 0 || K <= 0 || (N % 8) != 0 || (K % kGroup) != 0) return KAIROS_ERR_SHAPE;
     if (M == 0) return KAIROS_OK;
     if (!X || !qweight || !scales || !scaled_zeros || !Y || ((uintptr_t)X & 15) || ((uintptr_t)qweight & 15) ||
-        ((uintptr_t)Y & 1))
+        ((uintptr_t)scales & 15) || ((uintptr_t)scaled_zeros & 15) || ((uintptr_t)Y & 1))
         return KAIROS_ERR_ALIGN;
-    const int row_blocks = (N + kDecRows - 1) / kDecRows;
-    const int groups = K / kGroup;
-    // split K over a cluster while the grid is under two CTAs per SM and at least half the warps keep a group
-    int ksplit = 1;
-    const int sms = device_sm_count();
-    while (ksplit < 8 && row_blocks * ksplit < 2 * sms && groups / (ksplit * 2) >= kDecWarps / 2) ksplit *= 2;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(row_blocks * ksplit));
-    cfg.blockDim = dim3(kDecThreads);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)ksplit;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    const __half* x = static_cast<const __half*>(X);
-    const uint4* qw = static_cast<const uint4*>(qweight);
-    const __half* sc = static_cast<const __half*>(scales);
-    const __half* sz = static_cast<const __half*>(scaled_zeros);
-    const __half* b = static_cast<const __half*>(bias);
-    __half* y = static_cast<__half*>(Y);
-    cudaError_t e;
-    if (M <= 8)
-        e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<1>, x, qw, sc, sz, b, y, M, N, K, ksplit);
-    else
-        e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<2>, x, qw, sc, sz, b, y, M, N, K, ksplit);
-    if (e != cudaSuccess) return note_cuda_error(e);
-    return launch_status();
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (M <= 8) return launch_decode<1>(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, st);
+    return launch_decode<2>(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, st);
 }

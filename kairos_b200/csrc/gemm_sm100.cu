@@ -485,37 +485,16 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
 // ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    });
-    return fn;
-}
+int make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle);   // tensormap.cu
 
 // 2-D row-major tensor [rows, cols] of `elem_bytes` elements; box = box_cols x box_rows, no swizzle.
 static int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
                         uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return note_cuda_error(cudaErrorNotSupported);
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
-    const cuuint32_t box[2] = {box_cols, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return note_cuda_error(cudaErrorInvalidValue);
-    return KAIROS_OK;
+    const uint64_t dims[2] = {cols, rows};
+    const uint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+    const uint32_t box[2] = {box_cols, box_rows};
+    return make_tmap(map, dt, 2, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 // Row-major operand [rows, K] seen as k blocks of 128 bytes: dims {128 B of K, rows, K / block};
@@ -523,19 +502,12 @@ static int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType 
 // K-major tile [box_rows][128 B] (the layout tcgen05.mma reads), tiles back to back.
 static int make_tmap_kblocks(CUtensorMap* map, const void* base, bool int8, uint64_t rows, uint64_t K,
                              uint32_t box_rows, uint32_t box_kb) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return note_cuda_error(cudaErrorNotSupported);
     const uint64_t es = int8 ? 1 : 2, bk = int8 ? 128 : 64;
-    const cuuint64_t dims[3] = {bk, rows, K / bk};
-    const cuuint64_t strides[2] = {K * es, 128};
-    const cuuint32_t box[3] = {(cuuint32_t)bk, box_rows, box_kb};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = fn(map, int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return note_cuda_error(cudaErrorInvalidValue);
-    return KAIROS_OK;
+    const uint64_t dims[3] = {bk, rows, K / bk};
+    const uint64_t strides[2] = {K * es, 128};
+    const uint32_t box[3] = {(uint32_t)bk, box_rows, box_kb};
+    return make_tmap(map, int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims,
+                     strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 int device_sm_count() {

@@ -5,8 +5,8 @@ Mirrors kairos/perf_profiler.py:24-165 of the reference: ``Profiler(shape_list)`
 ``record_best_comp``, attributes ``seg_perf_list`` and ``lut``.  The LUT itself is the native
 C++ table of the shared library (reference: kernels/csrc/kairos_kernel/lut/lut.h).
 
-Timing is on-device (CUDA events around n back-to-back ``_forward`` calls after warm-up,
-as utils/perf_eval.py:21-34) and INCLUDES activation quantization and weight conversion.
+Timing is on-device (CUDA events around a CUDA graph of ``_forward`` calls that rotate over copies
+of the layer, after warm-up) and INCLUDES activation quantization and weight conversion.
 With ``cache='cold'`` (default) every timed call converts the weight again, which is what a
 layer sees when the model's converted weights do not fit the bounded cache; ``cache='warm'``
 times the steady state of a layer whose converted weight stays cached.
@@ -137,20 +137,52 @@ def collapse_segments(perf_list):
 
 
 @torch.no_grad()
-def time_forward(layer, x, m, comp_id, n, warmup):
-    """Mean milliseconds of one ``_forward`` over n back-to-back calls (CUDA events,
-    utils/perf_eval.py:21-34 of the reference)."""
-    for _ in range(warmup):
-        layer._forward(x, m, comp_id)
+def time_forward(layers, x, m, comp_id, n, warmup):
+    """Mean milliseconds of one ``_forward``.  The calls go round-robin over `layers` (copies of one
+    layer in distinct memory, so that the weights stream from HBM as they do inside a model rather than
+    sit in L2), are captured into one CUDA graph and the graph is replayed between two events: device
+    time without host launch gaps.  Falls back to an eager loop (utils/perf_eval.py:21-34 of the
+    reference) if capture is not possible."""
+    stream = torch.cuda.Stream()
+    rounds = max(1, n // len(layers))
+    with torch.cuda.stream(stream):
+        for _ in range(max(1, warmup // len(layers)) + 1):
+            for layer in layers:
+                layer._forward(x, m, comp_id)
     torch.cuda.synchronize()
     start = torch.cuda.Event(enable_timing=True)
     end = torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(n):
-        layer._forward(x, m, comp_id)
-    end.record()
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for layer in layers:
+                layer._forward(x, m, comp_id)
+        graph.replay()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(rounds):
+            graph.replay()
+        end.record()
+    except Exception:
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(rounds):
+            for layer in layers:
+                layer._forward(x, m, comp_id)
+        end.record()
     torch.cuda.synchronize()
-    return start.elapsed_time(end) / n
+    return start.elapsed_time(end) / (rounds * len(layers))
+
+
+def _clone_layer(layer, ctx):
+    """A copy of `layer` whose resident tensors live in fresh memory, bound to context `ctx`."""
+    twin = type(layer)(layer.in_features, layer.out_features, layer.bias is not None, layer.qweight.device, 128)
+    for name in ('qweight', 'scales', 'scaled_zeros', 'scales_to8', 'scaled_zeros_to8', 'scales_1'):
+        getattr(twin, name).copy_(getattr(layer, name))
+    if layer.bias is not None:
+        twin.bias.copy_(layer.bias)
+    twin._cache_context = lambda: ctx
+    return twin
 
 
 @torch.no_grad()
@@ -168,7 +200,12 @@ def test_perf(proj_name, K, N, bias, m_grid=None, candidates=None, n=200, warmup
     # cold: a zero-byte cache converts into one reusable slot on every call (no allocator traffic);
     # warm: a private unbounded cache keeps the converted weight after the first call
     own_ctx = Context(layer.qweight.device, cache_bytes=0 if cache == 'cold' else None)
+    own_ctx.reserve(max(m_grid), N, K)
     layer._cache_context = lambda: own_ctx
+    # enough copies of the layer that a round over them touches more packed weight than twice the L2
+    l2 = torch.cuda.get_device_properties(layer.qweight.device).L2_cache_size
+    copies = max(2, min(64, int(2.5 * l2 / (K * N // 2)) + 1))
+    layers = [layer] + [_clone_layer(layer, own_ctx) for _ in range(copies - 1)]
     table, perf_list = {}, []
     for m in m_grid:
         x = torch.randn((m, K), dtype=torch.float16, device=device)
@@ -177,7 +214,7 @@ def test_perf(proj_name, K, N, bias, m_grid=None, candidates=None, n=200, warmup
         for name in candidates:
             if m > 32 and 'gemv' in name:
                 continue
-            t = time_forward(layer, x, m, COMP_TYPE_NAME[name], n, warmup)
+            t = time_forward(layers, x, m, COMP_TYPE_NAME[name], n, warmup)
             table[m][name] = t
             if t < best_t:
                 best_t, best = t, name
@@ -186,5 +223,6 @@ def test_perf(proj_name, K, N, bias, m_grid=None, candidates=None, n=200, warmup
         perf_list.append((m, best, (orig_t - best_t) * 100 / orig_t))
         if verbose:
             print(f'{proj_name} m={m:6d} ' + ' '.join(f'{k}={v * 1e3:8.1f}us' for k, v in table[m].items()))
-    layer._release()
+    for lyr in layers:
+        lyr._release()
     return collapse_segments(perf_list), table
