@@ -32,6 +32,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 SHAPES_KN = [(4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)]       # (K, N)
+# the projection each shape stands for under tensor parallelism (o and down are row-parallel)
+SHAPE_ROLE = {(4096, 4096): 'o_proj', (4096, 1024): 'k_proj', (4096, 14336): 'gate_proj', (14336, 4096): 'down_proj'}
 M_LIST = [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192]
 METRIC = 'switched-linear TFLOPS over the Llama-3-8B shape x M sweep'
 
@@ -179,7 +181,7 @@ def build_layers(torch, kb, tp, rank, world, device):
         _, w = make_case(1, k, n, seed=0)
         w = torch.from_numpy(w)
         if world > 1:
-            layers.append(tp.shard_linear(w, kind=tp.layer_kind(k, n), rank=rank, world=world, device=device))
+            layers.append(tp.shard_linear(w, kind=tp.layer_kind(SHAPE_ROLE[(k, n)]), rank=rank, world=world, device=device))
         else:
             lin = torch.nn.Linear(k, n, bias=False, dtype=torch.float16)
             lin.weight.data = w
@@ -193,7 +195,7 @@ def make_inputs(torch, device, world, rank, tp):
     for (k, n) in SHAPES_KN:
         x, _ = make_case(max(M_LIST), k, 4, seed=1)
         x = torch.from_numpy(x)
-        if world > 1 and tp.layer_kind(k, n) == 'row':
+        if world > 1 and tp.layer_kind(SHAPE_ROLE[(k, n)]) == 'row':
             ks = k // world
             x = x[:, rank * ks:(rank + 1) * ks].contiguous()
         xs[(k, n)] = x
@@ -328,7 +330,8 @@ def run_gpu_arm(args):
         return ms / args.steps
 
     # The step as a CUDA graph: one pass of module forwards captured once, replayed per step (launch
-    # latency of the 56 small calls is then off the critical path).  NCCL collectives stay eager at N > 1.
+    # latency of the 56 small calls is then off the critical path).  At N > 1 the pass stays eager: the
+    # NCCL all-reduces are not captured.
     step_fn, mode = one_pass, 'eager'
     if world == 1:
         try:
@@ -432,7 +435,7 @@ def run_gpu_arm(args):
                           'bounded cache); the cold-cache LUT is reported per point as lut_cold',
                    'cache_bytes': cache_bytes, 'profile_seconds': round(t_prof, 1)},
         'e2e': {'value': total_flops / (ms_e2e * 1e-3) / 1e12, 'unit': 'TFLOPS',
-                'h2d_bytes_per_step': sum(2 * m * (k // world if tp and tp.layer_kind(k, n) == 'row' else k)
+                'h2d_bytes_per_step': sum(2 * m * (k // world if tp and tp.layer_kind(SHAPE_ROLE[(k, n)]) == 'row' else k)
                                           for (k, n) in SHAPES_KN for m in M_LIST),
                 'd2h_bytes_per_step': sum(2 * m * n for (k, n) in SHAPES_KN for m in M_LIST),
                 'ms_per_step': ms_e2e},

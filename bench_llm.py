@@ -1,0 +1,56 @@
+#!/usr/bin/env python
+"""TTFT / TPOT of a random-init decoder whose linears are switched linears (BASELINE configs 2-3).
+
+    python bench_llm.py --model llama3-8b --batches 2,4,8,16,32 --prompt 1024 --new 512
+
+Prints one JSON line per batch size: ttft_ms, tpot_ms, tokens_per_s, plus the LUT in use.  Protocol of
+the reference (utils/perf_eval.py:236-275): warm-up generations, TTFT = mean prefill + first token,
+TPOT = (t_generate - TTFT) / (new - 1).  Prompts are uniform random token ids (no dataset needed).
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--model', default='llama3-8b')
+    ap.add_argument('--batches', default='2,4,8,16,32')
+    ap.add_argument('--prompt', type=int, default=1024)
+    ap.add_argument('--new', type=int, default=512)
+    ap.add_argument('--layers', type=int, default=None, help='build only the first L layers (smoke runs)')
+    ap.add_argument('--cache-gb', type=float, default=24.0, help='bound of the conversion cache')
+    ap.add_argument('--lut', default='warm', choices=['warm', 'cold'])
+    args = ap.parse_args()
+
+    import torch
+    import kairos_b200 as kb
+    from kairos_b200 import llm, runtime
+
+    torch.cuda.set_device(0)
+    cfg = llm.PRESETS[args.model]
+    ctx = runtime.Context('cuda:0', cache_bytes=int(args.cache_gb * (1 << 30)))
+    kb.DynamicLinear.context = ctx
+    t0 = time.perf_counter()
+    prof = llm.build_lut(cfg, cache=args.lut)
+    t_lut = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    model = llm.Decoder(cfg, 'cuda:0', layers=args.layers)
+    t_build = time.perf_counter() - t0
+    lut = {str(s): [(r, name) for r, name, _ in prof.seg_perf_list[i]] for i, s in enumerate(prof.shape_list)}
+    print(json.dumps({'model': cfg.name, 'layers': len(model.model.layers), 'lut_seconds': round(t_lut, 1),
+                      'build_seconds': round(t_build, 1), 'lut_mode': args.lut, 'lut': lut,
+                      'weights_gb': round(sum(b.numel() * b.element_size() for b in model.buffers()) / 2**30, 2)}))
+    for b in [int(v) for v in args.batches.split(',')]:
+        r = llm.measure_ttft_tpot(model, b, args.prompt, args.new)
+        r.update({'model': cfg.name, 'cache': ctx.stats(), 'peak_gb': round(torch.cuda.max_memory_allocated() / 2**30, 2)})
+        print(json.dumps(r), flush=True)
+
+
+if __name__ == '__main__':
+    main()

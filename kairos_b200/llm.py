@@ -1,0 +1,296 @@
+"""Random-init decoder harness around the switched linear: the measurement vehicle for TTFT / TPOT.
+
+The reference measures end to end with a HuggingFace Llama/Qwen checkpoint and ``generate()``
+(utils/perf_eval.py:236-275, kairos/main_ablation.py:108-140).  Checkpoints are not available here,
+so this module builds the same decoder geometry with random weights (N(0, 0.02)), swaps every linear of
+the decoder layers through ``quantize_model`` exactly as the reference does (lm_head stays fp16), and
+runs prefill + greedy decode with a static KV cache.  Everything that is not a linear (RMSNorm, RoPE,
+attention, SiLU) is stock torch, as it is stock HuggingFace code in the reference.  The decode step is
+captured into a CUDA graph, so the per-token host cost is one graph launch.
+"""
+from __future__ import annotations
+
+import math
+import time
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from .dynamic_linear import DynamicLinear
+from .perf_profiler import Profiler
+from .quant_model import quantize_model
+
+
+@dataclass
+class DecoderConfig:
+    name: str
+    layers: int
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    inter: int
+    vocab: int
+    rms_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    qkv_bias: bool = False
+
+    def linear_shapes(self):
+        """Distinct (N, K) of the decoder linears, the key set of the profiler's LUT."""
+        q = self.n_heads * self.head_dim
+        kv = self.n_kv_heads * self.head_dim
+        shapes = [(q, self.hidden), (kv, self.hidden), (self.hidden, q), (self.inter, self.hidden),
+                  (self.hidden, self.inter)]
+        return list(dict.fromkeys(shapes))
+
+
+LLAMA3_8B = DecoderConfig('llama3-8b', 32, 4096, 32, 8, 128, 14336, 128256, 1e-5, 500000.0, False)
+QWEN2_7B = DecoderConfig('qwen2-7b', 28, 3584, 28, 4, 128, 18944, 152064, 1e-6, 1e6, True)
+LLAMA3_70B = DecoderConfig('llama3-70b', 80, 8192, 64, 8, 128, 28672, 128256, 1e-5, 500000.0, False)
+PRESETS = {c.name: c for c in (LLAMA3_8B, QWEN2_7B, LLAMA3_70B)}
+
+
+class RMSNorm(torch.nn.Module):
+    def __init__(self, dim, eps, device):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.ones(dim, dtype=torch.float16, device=device), requires_grad=False)
+        self.eps = eps
+
+    def forward(self, x):
+        v = x.float()
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)
+        return (v * self.weight.float()).to(torch.float16)
+
+
+class Attention(torch.nn.Module):
+    def __init__(self, cfg, device):
+        super().__init__()
+        h, q, kv = cfg.hidden, cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+        mk = dict(dtype=torch.float16, device=device)
+        self.q_proj = torch.nn.Linear(h, q, bias=cfg.qkv_bias, **mk)
+        self.k_proj = torch.nn.Linear(h, kv, bias=cfg.qkv_bias, **mk)
+        self.v_proj = torch.nn.Linear(h, kv, bias=cfg.qkv_bias, **mk)
+        self.o_proj = torch.nn.Linear(q, h, bias=False, **mk)
+        self.cfg = cfg
+
+
+class MLP(torch.nn.Module):
+    def __init__(self, cfg, device):
+        super().__init__()
+        mk = dict(dtype=torch.float16, device=device)
+        self.gate_proj = torch.nn.Linear(cfg.hidden, cfg.inter, bias=False, **mk)
+        self.up_proj = torch.nn.Linear(cfg.hidden, cfg.inter, bias=False, **mk)
+        self.down_proj = torch.nn.Linear(cfg.inter, cfg.hidden, bias=False, **mk)
+
+
+class DecoderLayer(torch.nn.Module):
+    def __init__(self, cfg, device):
+        super().__init__()
+        self.self_attn = Attention(cfg, device)
+        self.mlp = MLP(cfg, device)
+        self.input_layernorm = RMSNorm(cfg.hidden, cfg.rms_eps, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden, cfg.rms_eps, device)
+
+
+class _Inner(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.layers = torch.nn.ModuleList()
+
+
+def _rope_tables(cfg, max_len, device):
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device, dtype=torch.float32) / cfg.head_dim))
+    ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+    return torch.cos(ang).to(torch.float16), torch.sin(ang).to(torch.float16)      # [max_len, d/2]
+
+
+def _apply_rope(x, cos, sin):
+    # x [B, S, H, D]; cos/sin [S, D/2] (rotate-half convention)
+    d = x.shape[-1] // 2
+    x1, x2 = x[..., :d], x[..., d:]
+    c, s = cos[None, :, None, :], sin[None, :, None, :]
+    return torch.cat((x1 * c - x2 * s, x2 * c + x1 * s), dim=-1)
+
+
+class Decoder(torch.nn.Module):
+    """``model.model.layers`` holds the decoder layers (the attribute path ``quantize_model`` walks)."""
+
+    def __init__(self, cfg: DecoderConfig, device='cuda', seed=0, quant_strategy='DynamicLinear', layers=None):
+        super().__init__()
+        self.cfg = cfg
+        self.device = torch.device(device)
+        n_layers = cfg.layers if layers is None else layers
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        self.model = _Inner()
+        self.embed = (torch.randn((cfg.vocab, cfg.hidden), generator=gen, device=self.device, dtype=torch.float32)
+                      * 0.02).to(torch.float16)
+        self.lm_head = (torch.randn((cfg.vocab, cfg.hidden), generator=gen, device=self.device, dtype=torch.float32)
+                        * 0.02).to(torch.float16)
+        self.norm = RMSNorm(cfg.hidden, cfg.rms_eps, self.device)
+        # build and quantize layer by layer so that at most one fp16 layer is alive
+        for _ in range(n_layers):
+            layer = DecoderLayer(cfg, self.device)
+            for mod in layer.modules():
+                if isinstance(mod, torch.nn.Linear):
+                    mod.weight.data = (torch.randn(mod.weight.shape, generator=gen, device=self.device,
+                                                   dtype=torch.float32) * 0.02).to(torch.float16)
+                    if mod.bias is not None:
+                        mod.bias.data = (torch.randn(mod.bias.shape, generator=gen, device=self.device,
+                                                     dtype=torch.float32) * 0.02).to(torch.float16)
+            holder = _Inner()
+            holder.layers.append(layer)
+            wrap = torch.nn.Module()
+            wrap.model = holder
+            quantize_model(wrap, quant_strategy=quant_strategy, device=self.device)
+            self.model.layers.append(layer)
+        self.kv = None
+        self.graph = None
+
+    # ---- state ------------------------------------------------------------------------------
+    def allocate(self, batch, max_len, max_tokens=None):
+        """Static state for `batch` sequences of up to `max_len` positions.  `max_tokens` (default
+        batch * max_len) sizes the library's activation / split-K workspaces once, so that no later call
+        reallocates a buffer a captured CUDA graph still points to."""
+        cfg = self.cfg
+        from .runtime import default_context
+        ctx = DynamicLinear.context or default_context(self.device)
+        ctx.reserve(max_tokens or batch * max_len, max(s[0] for s in cfg.linear_shapes()),
+                    max(s[1] for s in cfg.linear_shapes()))
+        shape = (len(self.model.layers), 2, batch, cfg.n_kv_heads, max_len, cfg.head_dim)
+        self.kv = torch.zeros(shape, dtype=torch.float16, device=self.device)
+        self.max_len = max_len
+        self.cos, self.sin = _rope_tables(cfg, max_len, self.device)
+        # decode-step buffers (static addresses for the CUDA graph)
+        self.tok = torch.zeros((batch, 1), dtype=torch.long, device=self.device)
+        self.pos = torch.zeros((1,), dtype=torch.long, device=self.device)
+        self.mask = torch.full((1, 1, 1, max_len), float('-inf'), dtype=torch.float16, device=self.device)
+        self.next_tok = torch.zeros((batch, 1), dtype=torch.long, device=self.device)
+        self.graph = None
+
+    # ---- layers -----------------------------------------------------------------------------
+    def _layer(self, li, layer, x, pos0, decode):
+        cfg = self.cfg
+        b, s, _ = x.shape
+        h = layer.input_layernorm(x)
+        a = layer.self_attn
+        q = a.q_proj(h).view(b, s, cfg.n_heads, cfg.head_dim)
+        k = a.k_proj(h).view(b, s, cfg.n_kv_heads, cfg.head_dim)
+        v = a.v_proj(h).view(b, s, cfg.n_kv_heads, cfg.head_dim)
+        if decode:
+            cos, sin = self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos)
+        else:
+            cos, sin = self.cos[pos0:pos0 + s], self.sin[pos0:pos0 + s]
+        q = _apply_rope(q, cos, sin).transpose(1, 2)
+        k = _apply_rope(k, cos, sin).transpose(1, 2)
+        v = v.transpose(1, 2)
+        kc, vc = self.kv[li, 0], self.kv[li, 1]
+        if decode:
+            idx = self.pos.view(1, 1, 1, 1).expand(b, cfg.n_kv_heads, 1, cfg.head_dim)
+            kc.scatter_(2, idx, k)
+            vc.scatter_(2, idx, v)
+            o = F.scaled_dot_product_attention(q, kc, vc, attn_mask=self.mask, enable_gqa=True)
+        else:
+            kc[:, :, pos0:pos0 + s] = k
+            vc[:, :, pos0:pos0 + s] = v
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        o = o.transpose(1, 2).reshape(b, s, cfg.n_heads * cfg.head_dim)
+        x = x + a.o_proj(o)
+        h = layer.post_attention_layernorm(x)
+        m = layer.mlp
+        x = x + m.down_proj(F.silu(m.gate_proj(h)) * m.up_proj(h))
+        return x
+
+    @torch.no_grad()
+    def prefill(self, tokens):
+        """tokens [B, S] -> next token ids [B, 1]; fills the KV cache for positions 0..S-1."""
+        b, s = tokens.shape
+        x = self.embed[tokens]
+        for li, layer in enumerate(self.model.layers):
+            x = self._layer(li, layer, x, 0, False)
+        last = self.norm(x[:, -1:, :])
+        logits = last.reshape(b, -1) @ self.lm_head.t()
+        self.mask.fill_(float('-inf'))
+        self.mask[..., :s] = 0
+        self.pos.fill_(s)
+        return logits.argmax(dim=-1, keepdim=True)
+
+    def _decode_body(self):
+        x = self.embed[self.tok]
+        self.mask.index_fill_(3, self.pos, 0.0)
+        for li, layer in enumerate(self.model.layers):
+            x = self._layer(li, layer, x, 0, True)
+        logits = self.norm(x).reshape(x.shape[0], -1) @ self.lm_head.t()
+        self.next_tok.copy_(logits.argmax(dim=-1, keepdim=True))
+        self.pos.add_(1)
+
+    @torch.no_grad()
+    def decode_step(self, use_graph=True):
+        """One token for every sequence: reads self.tok, writes self.next_tok, advances self.pos."""
+        if not use_graph:
+            self._decode_body()
+            return
+        if self.graph is None:
+            pos0 = self.pos.clone()
+            mask0 = self.mask.clone()
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._decode_body()
+            torch.cuda.synchronize()
+            self.pos.copy_(pos0)
+            self.mask.copy_(mask0)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side):
+                self._decode_body()
+            self.pos.copy_(pos0)
+            self.mask.copy_(mask0)
+            torch.cuda.synchronize()
+        self.graph.replay()
+
+    @torch.no_grad()
+    def generate(self, tokens, max_new_tokens, use_graph=True):
+        nxt = self.prefill(tokens)
+        out = [nxt]
+        for _ in range(max_new_tokens - 1):
+            self.tok.copy_(nxt)
+            self.decode_step(use_graph)
+            nxt = self.next_tok.clone()
+            out.append(nxt)
+        return torch.cat(out, dim=1)
+
+
+@torch.no_grad()
+def measure_ttft_tpot(model, batch, prompt_len=1024, new_tokens=512, warmup=2, ttft_times=5, seed=0):
+    """TTFT = mean wall time of prefill + first token over `ttft_times` runs; TPOT = (time of a full
+    generation - TTFT) / (new_tokens - 1); throughput = batch * new_tokens / (TTFT + (new_tokens-1) * TPOT)
+    (utils/perf_eval.py:236-275 and kairos/main_ablation.py:111-125 of the reference)."""
+    dev = model.device
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    tokens = torch.randint(0, model.cfg.vocab, (batch, prompt_len), generator=gen, device=dev)
+    model.allocate(batch, prompt_len + new_tokens + 8)
+    for _ in range(warmup):
+        model.generate(tokens, 4)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(ttft_times):
+        model.prefill(tokens)
+        torch.cuda.synchronize()
+    ttft = (time.perf_counter() - t0) / ttft_times
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = model.generate(tokens, new_tokens)
+    torch.cuda.synchronize()
+    total = time.perf_counter() - t0
+    tpot = (total - ttft) / (new_tokens - 1)
+    return {'batch': batch, 'prompt_len': prompt_len, 'new_tokens': int(out.shape[1]), 'ttft_ms': 1e3 * ttft,
+            'tpot_ms': 1e3 * tpot, 'tokens_per_s': batch * new_tokens / (ttft + (new_tokens - 1) * tpot)}
+
+
+def build_lut(cfg, device='cuda', m_grid=None, cache='warm', n=20):
+    """Profile the decoder's linear shapes on the device and install the LUT on DynamicLinear."""
+    grid = m_grid or [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192, 16384, 32768]
+    prof = Profiler(cfg.linear_shapes(), m_grid=grid, n=n, warmup=3, cache=cache)
+    prof.profiling(device=device)
+    DynamicLinear.prof = prof
+    return prof

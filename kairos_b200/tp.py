@@ -17,10 +17,15 @@ import torch.distributed as dist
 from .dynamic_linear import DynamicLinear
 
 
-def layer_kind(k, n):
-    """Split rule by geometry: projections that shrink or keep the width (o_proj K == N,
-    down_proj K > N) are row-parallel, the expanding ones (k/v, gate/up) column-parallel."""
-    return 'row' if k >= n else 'col'
+# Megatron split of a decoder layer's linears: the projections that read the replicated hidden state
+# are column-parallel, the two that produce it are row-parallel (one all-reduce each).
+LAYER_KIND = {'q_proj': 'col', 'k_proj': 'col', 'v_proj': 'col', 'gate_proj': 'col', 'up_proj': 'col',
+              'o_proj': 'row', 'down_proj': 'row'}
+
+
+def layer_kind(name):
+    """'col' or 'row' for a projection name such as 'self_attn.o_proj' or 'down_proj'."""
+    return LAYER_KIND[name.split('.')[-1]]
 
 
 def shard_bounds(size, rank, world, multiple):

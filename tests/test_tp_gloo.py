@@ -1,0 +1,98 @@
+"""Tensor-parallel host logic on CPU: two gloo ranks shard a layer column- and row-wise, run their
+shards (the per-rank compute is the CPU oracle here, standing in for the CUDA layer), all-reduce the
+row-parallel partials and must agree with the per-shard oracle sum and, loosely, with the unsharded
+layer."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import kairos_oracle as ko
+
+
+class OracleLinear(torch.nn.Module):
+    """Test stand-in with the DynamicLinear interface: quantizes its fp16 weight like from_module and
+    evaluates kernel id 0 with the numpy oracle."""
+
+    def __init__(self, weight):
+        super().__init__()
+        self.res = ko.from_module(weight.numpy())
+        self.shape = tuple(weight.shape)
+        self.qweight = torch.from_numpy(self.res['qweight'])
+
+    @classmethod
+    def from_module(cls, linear, device, **_):
+        return cls(linear.weight.data)
+
+    def forward(self, x):
+        shape = x.shape
+        y = ko.y_w4a16(x.reshape(-1, shape[-1]).numpy(), self.res)
+        return torch.from_numpy(y).reshape(*shape[:-1], -1)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(('127.0.0.1', 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    from kairos_b200 import tp
+    x, w = ko.make_case(6, 512, 256, seed=9)
+    xt, wt = torch.from_numpy(x), torch.from_numpy(w)
+    # column parallel: replicated input, sharded output, gathered for the check
+    col = tp.shard_linear(wt, 'col', rank, world, 'cpu', linear_cls=OracleLinear)
+    col.gather_output = True
+    y_col = col(xt.unsqueeze(0))[0]
+    # row parallel: sharded input, all-reduced output
+    row = tp.shard_linear(wt, 'row', rank, world, 'cpu', linear_cls=OracleLinear)
+    ks = 512 // world
+    y_row = row(xt[:, rank * ks:(rank + 1) * ks].contiguous().unsqueeze(0))[0]
+    if rank == 0:
+        out['y_col'] = y_col.numpy()
+        out['y_row'] = y_row.numpy()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_column_and_row_parallel():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    x, w = ko.make_case(6, 512, 256, seed=9)
+    # expected: every rank quantizes its own shard
+    col_parts = [ko.y_w4a16(x, ko.from_module(w[r * 128:(r + 1) * 128])) for r in range(world)]
+    assert np.array_equal(out['y_col'].view(np.uint16), np.concatenate(col_parts, axis=1).view(np.uint16))
+    row_parts = [ko.y_w4a16(x[:, r * 256:(r + 1) * 256], ko.from_module(np.ascontiguousarray(w[:, r * 256:(r + 1) * 256])))
+                 for r in range(world)]
+    expect = (row_parts[0].astype(np.float32) + row_parts[1].astype(np.float32)).astype(np.float16)
+    bad, _ = ko.within_tolerance(out['y_row'], expect)
+    assert bad == 0
+    # and both are close to the unquantized product (quantization noise only)
+    ref = (x.astype(np.float32) @ w.astype(np.float32).T)
+    for y in (out['y_col'], out['y_row']):
+        rel = np.abs(y.astype(np.float32) - ref).sum() / np.abs(ref).sum()
+        assert rel < 0.2
+
+
+def test_shard_rules():
+    from kairos_b200 import tp
+    assert tp.layer_kind('self_attn.o_proj') == 'row' and tp.layer_kind('mlp.down_proj') == 'row'
+    assert all(tp.layer_kind(n) == 'col' for n in ('q_proj', 'k_proj', 'v_proj', 'gate_proj', 'mlp.up_proj'))
+    w = torch.zeros(64, 512, dtype=torch.float16)
+    assert tp.shard_weight(w, 'col', 1, 4).shape == (16, 512)
+    assert tp.shard_weight(w, 'row', 3, 4).shape == (64, 128)
+    with pytest.raises(ValueError):
+        tp.shard_weight(w, 'row', 0, 8)           # 64-wide K shards would split a quantization group
+    with pytest.raises(ValueError):
+        tp.shard_weight(torch.zeros(20, 512), 'col', 0, 8)

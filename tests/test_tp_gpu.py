@@ -1,0 +1,73 @@
+"""Tensor parallelism on real GPUs (needs two): NCCL all-reduce after the row-parallel layer, per-rank
+quantization, per-rank kernels; checked against the per-shard oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import kairos_oracle as ko
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(('127.0.0.1', 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    os.environ['NCCL_NVLS_ENABLE'] = '0'
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    import kairos_b200 as kb
+    from kairos_b200 import tp
+    dev = torch.device('cuda', rank)
+    x, w = ko.make_case(24, 1024, 512, seed=13)
+    xt, wt = torch.from_numpy(x), torch.from_numpy(w)
+    col = tp.shard_linear(wt, 'col', rank, world, dev)
+    row = tp.shard_linear(wt, 'row', rank, world, dev)
+    prof = kb.Profiler([col.linear.shape, row.linear.shape])
+    prof.load_table({col.linear.shape: [(8, 'w4a16_gemv'), (30720, 'w4a16_gemm')],
+                     row.linear.shape: [(8, 'w4a16_gemv'), (30720, 'w8a8')]})
+    kb.DynamicLinear.prof = prof
+    col.gather_output = True
+    ks = 1024 // world
+    res = {}
+    for m in (4, 24):
+        xm = xt[:m].to(dev)
+        res[f'col{m}'] = col(xm.unsqueeze(0))[0].cpu().numpy()
+        res[f'row{m}'] = row(xm[:, rank * ks:(rank + 1) * ks].contiguous().unsqueeze(0))[0].cpu().numpy()
+    torch.cuda.synchronize()
+    if rank == 0:
+        out.update(res)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_two_gpu_tensor_parallel_matches_per_shard_oracle():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    x, w = ko.make_case(24, 1024, 512, seed=13)
+    for m in (4, 24):
+        xm = x[:m]
+        col = np.concatenate([ko.y_w4a16(xm, ko.from_module(w[r * 256:(r + 1) * 256])) for r in range(world)], axis=1)
+        bad, _ = ko.within_tolerance(out[f'col{m}'], col)
+        assert bad == 0, f'column parallel m={m}'
+        comp = 1 if m <= 8 else 2
+        parts = [ko.forward(xm[:, r * 512:(r + 1) * 512], ko.from_module(np.ascontiguousarray(w[:, r * 512:(r + 1) * 512])), comp)
+                 for r in range(world)]
+        row = (parts[0].astype(np.float32) + parts[1].astype(np.float32)).astype(np.float16)
+        bad, _ = ko.within_tolerance(out[f'row{m}'], row)
+        assert bad == 0, f'row parallel m={m}'
