@@ -307,7 +307,7 @@ def run_gpu_arm(args):
 
     total_flops = sum(2 * m * k * n for (k, n) in SHAPES_KN for m in M_LIST)
 
-    def timed(fn):
+    def timed(fn, mark=False):
         for _ in range(max(3, args.warmup)):
             fn()
         torch.cuda.synchronize()
@@ -315,11 +315,15 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if mark:
+            torch.cuda.profiler.start()      # lets `ncu --profile-from-start off` see exactly the timed steps
         s.record()
         for _ in range(args.steps):
             fn()
         e.record()
         torch.cuda.synchronize()
+        if mark:
+            torch.cuda.profiler.stop()
         if world > 1:
             dist.barrier()
         ms = s.elapsed_time(e)
@@ -352,7 +356,7 @@ def run_gpu_arm(args):
     if rank == 0:
         sampler.start()
     stats0 = ctx.stats()
-    ms_step = timed(step_fn)
+    ms_step = timed(step_fn, mark=True)
     stats1 = ctx.stats()
     clocks = None
     if rank == 0:
@@ -458,6 +462,15 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
+# under profiles/ (same kernels, same shapes as the roofline points below); bytes.
+NCU_TRAFFIC = {
+    'umma_gemm_kernel<int8, tma, BT=256>': 94454784 + 202956288,     # profiles/umma_gemm_int8_M8192_K4096_N14336.md
+    'umma_gemm_kernel<f16, tma, BT=256>': 1334805000 + 228701184,    # profiles/umma_gemm_f16_M8192_K4096_N14336.md
+    'decode': 31218432,                                              # profiles/decode_mma_M1_K4096_N14336.md
+}
+
+
 def dominant_rooflines(torch, kb, mods, xs_dev, prof, peaks, flush, l2_bytes):
     """Roofline of the kernel that dominates the pass (the M=8192 GEMM of the gate/up shape, in
     the precision the LUT chose) and of the decode kernel at M=1 on the same shape."""
@@ -509,7 +522,7 @@ def dominant_rooflines(torch, kb, mods, xs_dev, prof, peaks, flush, l2_bytes):
         kern = 'umma_gemm_kernel<f16, w4-expand, BT=256>'
     ach = 2 * m * k * n / t / 1e12
     roof = {'bound': 'tensor', 'kernel': kern, 'lut_choice': name, 'point': {'M': m, 'K': k, 'N': n},
-            'achieved': ach, 'peak': peak, 'unit': 'TFLOP/s', 'frac': ach / peak, 'traffic': None,
+            'achieved': ach, 'peak': peak, 'unit': 'TFLOP/s', 'frac': ach / peak, 'traffic': NCU_TRAFFIC.get(kern),
             'peak_source': f'{peaks["source"]}: {peak_note}', 'us_per_launch': t * 1e6}
     x1 = xs_dev[(k, n)][:1]
     rot = RotatingWeights(torch, mod, l2_bytes)
@@ -518,7 +531,8 @@ def dominant_rooflines(torch, kb, mods, xs_dev, prof, peaks, flush, l2_bytes):
     ach1 = algorithmic_bytes(1, k, n) / us1 / 1e3
     roof_gemv = {'bound': 'hbm', 'kernel': 'decode_mma_kernel<1> (kernel id 1 at M=1)', 'point': {'M': 1, 'K': k, 'N': n},
                  'achieved': ach1, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s', 'frac': ach1 / peaks['hbm_gbs'],
-                 'traffic': None, 'peak_source': f'{peaks["source"]}: stream copy', 'us_per_launch': us1,
+                 'traffic': NCU_TRAFFIC['decode'], 'algorithmic_bytes': algorithmic_bytes(1, k, n),
+                 'peak_source': f'{peaks["source"]}: stream copy', 'us_per_launch': us1,
                  'timing': f'CUDA graph over {rot.n} weight copies (> 2x L2)'}
     return roof, roof_gemv
 
