@@ -26,6 +26,8 @@ def main():
     ap.add_argument('--layers', type=int, default=None, help='build only the first L layers (smoke runs)')
     ap.add_argument('--cache-gb', type=float, default=24.0, help='bound of the conversion cache')
     ap.add_argument('--lut', default='warm', choices=['warm', 'cold'])
+    ap.add_argument('--no-fuse', action='store_true', help='keep q/k/v and gate/up as separate linears (7 per layer)')
+    ap.add_argument('--glue', default='cuda', choices=['cuda', 'torch'], help="'torch' = stock torch ops around the linears")
     args = ap.parse_args()
 
     import torch
@@ -37,14 +39,14 @@ def main():
     ctx = runtime.Context('cuda:0', cache_bytes=int(args.cache_gb * (1 << 30)))
     kb.DynamicLinear.context = ctx
     t0 = time.perf_counter()
-    prof = llm.build_lut(cfg, cache=args.lut)
-    t_lut = time.perf_counter() - t0
-    t0 = time.perf_counter()
-    model = llm.Decoder(cfg, 'cuda:0', layers=args.layers)
+    model = llm.Decoder(cfg, 'cuda:0', layers=args.layers, fuse_linears=not args.no_fuse, glue=args.glue)
     t_build = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    prof = llm.build_lut(model.linear_shapes(), cache=args.lut)
+    t_lut = time.perf_counter() - t0
     lut = {str(s): [(r, name) for r, name, _ in prof.seg_perf_list[i]] for i, s in enumerate(prof.shape_list)}
     print(json.dumps({'model': cfg.name, 'layers': len(model.model.layers), 'lut_seconds': round(t_lut, 1),
-                      'build_seconds': round(t_build, 1), 'lut_mode': args.lut, 'lut': lut,
+                      'build_seconds': round(t_build, 1), 'lut_mode': args.lut, 'lut': lut, 'fused_linears': not args.no_fuse, 'glue': args.glue,
                       'weights_gb': round(sum(b.numel() * b.element_size() for b in model.buffers()) / 2**30, 2)}))
     for b in [int(v) for v in args.batches.split(',')]:
         r = llm.measure_ttft_tpot(model, b, args.prompt, args.new)

@@ -144,6 +144,22 @@ int kairos_w8a8_gemm(const void* Xq_i8, const void* W8, const void* scales_1, co
 int kairos_f16_gemm(const void* X_f16, const void* W16, const void* bias_f16_or_null, void* Y_f16, int M, int N,
                     int K, void* workspace, size_t workspace_bytes, kairos_stream_t stream);
 
+/* ---- element-wise operators around the linears of a decoder layer (one pass each) ----------------
+ * Counterparts the reference vendors but never calls: rms_norm_general
+ * (thirdparty/AWQ/kernels/csrc/w8a8/layernorm.cu:56-231) and silu_and_mul
+ * (thirdparty/AWQ/kernels/csrc/w8a8/act.cu:34-140); in its runs these steps are HuggingFace torch code. */
+/* Y[m,:] = half(float(X[m,:]) * rsqrt(mean(X[m,:]^2) + eps) * float(W)); K % 8 == 0, K <= 16384 */
+int kairos_rms_norm(const void* X_f16, const void* W_f16, void* Y_f16, int M, int K, float eps,
+                    kairos_stream_t stream);
+/* Y[m,i] = silu(GU[m,i]) * GU[m,I+i] for the fused gate|up activation GU [M, 2I]; I % 8 == 0 */
+int kairos_silu_mul(const void* GU_f16, void* Y_f16, int M, int I, kairos_stream_t stream);
+/* Rotary embedding (rotate-half) of the q and k heads of a fused QKV activation [B*S, (H+2Hkv)*D] plus the
+ * KV-cache write: Q_out [B,H,S,D], caches [B,Hkv,max_len,D]; token (b,s) is at position pos0 + s where
+ * pos0 = *pos_dev (int64 in device memory, for graph-replayed decode steps) or the host value. */
+int kairos_rope_kv(const void* QKV_f16, const void* cos_table, const void* sin_table, const void* pos_dev_or_null,
+                   int pos0, void* Q_out, void* K_cache, void* V_cache, int B, int S, int H, int Hkv, int D,
+                   int max_len, kairos_stream_t stream);
+
 /* ---- interval LUT: M -> kernel id  (kernels/csrc/kairos_kernel/lut/lut.h:8-43) ---- */
 typedef struct kairos_lut kairos_lut;
 kairos_lut* kairos_lut_create(void);

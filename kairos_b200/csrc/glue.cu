@@ -1,0 +1,165 @@
+// Element-wise operators that sit directly before / after the switched linears of a decoder layer,
+// each as ONE pass over the activations: RMSNorm, SiLU(gate) * up, and rotary embedding fused with the
+// KV-cache write.  The reference vendors (and never calls) rms_norm_general and silu_and_mul
+// (thirdparty/AWQ/kernels/csrc/w8a8/layernorm.cu:56-231, act.cu:34-140); in a stock torch / HuggingFace
+// decoder these steps are ~40 small kernels per layer and dominate both the decode step and the
+// non-GEMM part of prefill.  All are HBM-bound: 2 bytes read + 2 bytes written per element.
+#include "common.cuh"
+
+namespace kairos {
+
+// y = half( float(x) * rsqrt(mean(x^2) + eps) * float(w) ), one CTA per token, row kept in registers
+template <int R>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const __half* __restrict__ X, const __half* __restrict__ W,
+                                                       __half* __restrict__ Y, int K, float eps) {
+    const int token = blockIdx.x;
+    const int chunks = K >> 3;
+    const uint4* row = reinterpret_cast<const uint4*>(X + (size_t)token * K);
+    uint4 v[R];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int c = threadIdx.x + r * 256;
+        if (c < chunks) {
+            v[r] = __ldg(row + c);
+            const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                ss += f.x * f.x + f.y * f.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    __shared__ float part[8];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) ss += part[w];
+    const float inv = rsqrtf(ss / (float)K + eps);
+    uint4* out = reinterpret_cast<uint4*>(Y + (size_t)token * K);
+    const uint4* wv = reinterpret_cast<const uint4*>(W);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int c = threadIdx.x + r * 256;
+        if (c < chunks) {
+            const uint4 wq = __ldg(wv + c);
+            const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+            const __half2* g = reinterpret_cast<const __half2*>(&wq);
+            uint4 o4;
+            __half2* o = reinterpret_cast<__half2*>(&o4);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]), gw = __half22float2(g[i]);
+                o[i] = __floats2half2_rn(f.x * inv * gw.x, f.y * inv * gw.y);
+            }
+            out[c] = o4;
+        }
+    }
+}
+
+// Y[m, i] = half( half(silu(gate)) * up ), gate = GU[m, i], up = GU[m, I + i]
+__global__ void __launch_bounds__(256) silu_mul_kernel(const __half* __restrict__ GU, __half* __restrict__ Y, int M,
+                                                       int I) {
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;       // one 8-element chunk
+    const int per_row = I >> 3;
+    if (idx >= (long long)M * per_row) return;
+    const int m = (int)(idx / per_row), c = (int)(idx % per_row);
+    const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(GU + (size_t)m * 2 * I) + c);
+    const uint4 u4 = __ldg(reinterpret_cast<const uint4*>(GU + (size_t)m * 2 * I + I) + c);
+    const __half2* g = reinterpret_cast<const __half2*>(&g4);
+    const __half2* u = reinterpret_cast<const __half2*>(&u4);
+    uint4 o4;
+    __half2* o = reinterpret_cast<__half2*>(&o4);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(g[i]);
+        const __half2 s = __floats2half2_rn(f.x / (1.f + __expf(-f.x)), f.y / (1.f + __expf(-f.y)));
+        o[i] = __hmul2(s, u[i]);
+    }
+    reinterpret_cast<uint4*>(Y + (size_t)m * I)[c] = o4;
+}
+
+// Rotary embedding (rotate-half convention) of the q and k heads of a fused QKV activation and the
+// KV-cache write, one thread per pair (d, d + D/2) of one head of one token.
+//   QKV  [B*S, (H + 2 Hkv) * D]      Q_out [B, H, S, D]      cache K / V [B, Hkv, max_len, D]
+// Token (b, s) sits at position pos0 + s, with pos0 = *pos_dev when pos_dev is given (decode step whose
+// position lives in device memory so that a CUDA graph can be replayed) and pos0_host otherwise.
+__global__ void __launch_bounds__(256) rope_kv_kernel(const __half* __restrict__ QKV, const __half* __restrict__ cosT,
+                                                      const __half* __restrict__ sinT, const long long* pos_dev,
+                                                      int pos0_host, __half* __restrict__ Q_out,
+                                                      __half* __restrict__ Kc, __half* __restrict__ Vc, int B, int S,
+                                                      int H, int Hkv, int D, int max_len) {
+    const int half_d = D >> 1;
+    const int heads = H + 2 * Hkv;
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+    const long long total = (long long)B * S * heads * half_d;
+    if (idx >= total) return;
+    const int d = (int)(idx % half_d);
+    long long r = idx / half_d;
+    const int head = (int)(r % heads);
+    r /= heads;
+    const int s = (int)(r % S), b = (int)(r / S);
+    const int pos = (pos_dev ? (int)*pos_dev : pos0_host) + s;
+    const __half* src = QKV + ((size_t)(b * S + s) * heads + head) * D;
+    const float x1 = __half2float(src[d]), x2 = __half2float(src[d + half_d]);
+    if (head < H + Hkv) {
+        const float c = __half2float(cosT[(size_t)pos * half_d + d]), sn = __half2float(sinT[(size_t)pos * half_d + d]);
+        const __half y1 = __float2half_rn(x1 * c - x2 * sn), y2 = __float2half_rn(x2 * c + x1 * sn);
+        __half* dst = head < H ? Q_out + (((size_t)b * H + head) * S + s) * D
+                               : Kc + (((size_t)b * Hkv + (head - H)) * max_len + pos) * D;
+        dst[d] = y1;
+        dst[d + half_d] = y2;
+    } else {
+        __half* dst = Vc + (((size_t)b * Hkv + (head - H - Hkv)) * max_len + pos) * D;
+        dst[d] = src[d];
+        dst[d + half_d] = src[d + half_d];
+    }
+}
+
+}  // namespace kairos
+
+extern "C" int kairos_rms_norm(const void* X, const void* W, void* Y, int M, int K, float eps, kairos_stream_t stream) {
+    using namespace kairos;
+    if (M < 0 || K <= 0 || (K % 8) != 0 || K > 8 * 256 * 8) return KAIROS_ERR_SHAPE;
+    if (M == 0) return KAIROS_OK;
+    if (!X || !W || !Y || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)Y & 15)) return KAIROS_ERR_ALIGN;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const __half* x = static_cast<const __half*>(X);
+    const __half* w = static_cast<const __half*>(W);
+    __half* y = static_cast<__half*>(Y);
+    const int per = (K / 8 + 255) / 256;
+    if (per <= 1) rms_norm_kernel<1><<<M, 256, 0, st>>>(x, w, y, K, eps);
+    else if (per <= 2) rms_norm_kernel<2><<<M, 256, 0, st>>>(x, w, y, K, eps);
+    else if (per <= 4) rms_norm_kernel<4><<<M, 256, 0, st>>>(x, w, y, K, eps);
+    else rms_norm_kernel<8><<<M, 256, 0, st>>>(x, w, y, K, eps);
+    return launch_status();
+}
+
+extern "C" int kairos_silu_mul(const void* GU, void* Y, int M, int I, kairos_stream_t stream) {
+    using namespace kairos;
+    if (M < 0 || I <= 0 || (I % 8) != 0) return KAIROS_ERR_SHAPE;
+    if (M == 0) return KAIROS_OK;
+    if (!GU || !Y || ((uintptr_t)GU & 15) || ((uintptr_t)Y & 15)) return KAIROS_ERR_ALIGN;
+    const long long chunks = (long long)M * (I / 8);
+    silu_mul_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(GU), static_cast<__half*>(Y), M, I);
+    return launch_status();
+}
+
+extern "C" int kairos_rope_kv(const void* QKV, const void* cos_table, const void* sin_table, const void* pos_dev_or_null,
+                              int pos0, void* Q_out, void* K_cache, void* V_cache, int B, int S, int H, int Hkv, int D,
+                              int max_len, kairos_stream_t stream) {
+    using namespace kairos;
+    if (B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || D <= 0 || (D & 1) || max_len <= 0) return KAIROS_ERR_SHAPE;
+    if (!pos_dev_or_null && (pos0 < 0 || pos0 + S > max_len)) return KAIROS_ERR_SHAPE;
+    if (!QKV || !cos_table || !sin_table || !Q_out || !K_cache || !V_cache) return KAIROS_ERR_ALIGN;
+    const long long total = (long long)B * S * (H + 2 * Hkv) * (D / 2);
+    rope_kv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(QKV), static_cast<const __half*>(cos_table), static_cast<const __half*>(sin_table),
+        static_cast<const long long*>(pos_dev_or_null), pos0, static_cast<__half*>(Q_out),
+        static_cast<__half*>(K_cache), static_cast<__half*>(V_cache), B, S, H, Hkv, D, max_len);
+    return launch_status();
+}

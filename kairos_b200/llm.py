@@ -17,6 +17,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
+from . import ops
 from .dynamic_linear import DynamicLinear
 from .perf_profiler import Profiler
 from .quant_model import quantize_model
@@ -64,31 +65,38 @@ class RMSNorm(torch.nn.Module):
 
 
 class Attention(torch.nn.Module):
-    def __init__(self, cfg, device):
+    def __init__(self, cfg, device, fuse):
         super().__init__()
         h, q, kv = cfg.hidden, cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
         mk = dict(dtype=torch.float16, device=device)
-        self.q_proj = torch.nn.Linear(h, q, bias=cfg.qkv_bias, **mk)
-        self.k_proj = torch.nn.Linear(h, kv, bias=cfg.qkv_bias, **mk)
-        self.v_proj = torch.nn.Linear(h, kv, bias=cfg.qkv_bias, **mk)
+        if fuse:
+            # q, k and v read the same activation: one switched linear with the three weights stacked
+            # along N.  Quantization is per output row, so the result equals the three separate layers.
+            self.qkv_proj = torch.nn.Linear(h, q + 2 * kv, bias=cfg.qkv_bias, **mk)
+        else:
+            self.q_proj = torch.nn.Linear(h, q, bias=cfg.qkv_bias, **mk)
+            self.k_proj = torch.nn.Linear(h, kv, bias=cfg.qkv_bias, **mk)
+            self.v_proj = torch.nn.Linear(h, kv, bias=cfg.qkv_bias, **mk)
         self.o_proj = torch.nn.Linear(q, h, bias=False, **mk)
-        self.cfg = cfg
 
 
 class MLP(torch.nn.Module):
-    def __init__(self, cfg, device):
+    def __init__(self, cfg, device, fuse):
         super().__init__()
         mk = dict(dtype=torch.float16, device=device)
-        self.gate_proj = torch.nn.Linear(cfg.hidden, cfg.inter, bias=False, **mk)
-        self.up_proj = torch.nn.Linear(cfg.hidden, cfg.inter, bias=False, **mk)
+        if fuse:
+            self.gate_up_proj = torch.nn.Linear(cfg.hidden, 2 * cfg.inter, bias=False, **mk)
+        else:
+            self.gate_proj = torch.nn.Linear(cfg.hidden, cfg.inter, bias=False, **mk)
+            self.up_proj = torch.nn.Linear(cfg.hidden, cfg.inter, bias=False, **mk)
         self.down_proj = torch.nn.Linear(cfg.inter, cfg.hidden, bias=False, **mk)
 
 
 class DecoderLayer(torch.nn.Module):
-    def __init__(self, cfg, device):
+    def __init__(self, cfg, device, fuse):
         super().__init__()
-        self.self_attn = Attention(cfg, device)
-        self.mlp = MLP(cfg, device)
+        self.self_attn = Attention(cfg, device, fuse)
+        self.mlp = MLP(cfg, device, fuse)
         self.input_layernorm = RMSNorm(cfg.hidden, cfg.rms_eps, device)
         self.post_attention_layernorm = RMSNorm(cfg.hidden, cfg.rms_eps, device)
 
@@ -102,7 +110,7 @@ class _Inner(torch.nn.Module):
 def _rope_tables(cfg, max_len, device):
     inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device, dtype=torch.float32) / cfg.head_dim))
     ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
-    return torch.cos(ang).to(torch.float16), torch.sin(ang).to(torch.float16)      # [max_len, d/2]
+    return torch.cos(ang).to(torch.float16).contiguous(), torch.sin(ang).to(torch.float16).contiguous()
 
 
 def _apply_rope(x, cos, sin):
@@ -114,12 +122,18 @@ def _apply_rope(x, cos, sin):
 
 
 class Decoder(torch.nn.Module):
-    """``model.model.layers`` holds the decoder layers (the attribute path ``quantize_model`` walks)."""
+    """``model.model.layers`` holds the decoder layers (the attribute path ``quantize_model`` walks).
 
-    def __init__(self, cfg: DecoderConfig, device='cuda', seed=0, quant_strategy='DynamicLinear', layers=None):
+    fuse_linears: stack q|k|v and gate|up into one switched linear each (4 instead of 7 per layer).
+    glue: 'cuda' runs RMSNorm, rotary + KV write and SiLU*up as one library kernel each; 'torch' runs
+    them as stock torch ops (what a HuggingFace model does)."""
+
+    def __init__(self, cfg: DecoderConfig, device='cuda', seed=0, quant_strategy='DynamicLinear', layers=None,
+                 fuse_linears=True, glue='cuda'):
         super().__init__()
         self.cfg = cfg
         self.device = torch.device(device)
+        self.fuse, self.glue = fuse_linears, glue
         n_layers = cfg.layers if layers is None else layers
         gen = torch.Generator(device=self.device).manual_seed(seed)
         self.model = _Inner()
@@ -130,7 +144,7 @@ class Decoder(torch.nn.Module):
         self.norm = RMSNorm(cfg.hidden, cfg.rms_eps, self.device)
         # build and quantize layer by layer so that at most one fp16 layer is alive
         for _ in range(n_layers):
-            layer = DecoderLayer(cfg, self.device)
+            layer = DecoderLayer(cfg, self.device, fuse_linears)
             for mod in layer.modules():
                 if isinstance(mod, torch.nn.Linear):
                     mod.weight.data = (torch.randn(mod.weight.shape, generator=gen, device=self.device,
@@ -147,6 +161,14 @@ class Decoder(torch.nn.Module):
         self.kv = None
         self.graph = None
 
+    def linear_shapes(self):
+        """Distinct (N, K) of this model's switched linears (the LUT's key set)."""
+        shapes = []
+        for mod in self.model.layers[0].modules():
+            if isinstance(mod, DynamicLinear) and mod.shape not in shapes:
+                shapes.append(mod.shape)
+        return shapes
+
     # ---- state ------------------------------------------------------------------------------
     def allocate(self, batch, max_len, max_tokens=None):
         """Static state for `batch` sequences of up to `max_len` positions.  `max_tokens` (default
@@ -155,8 +177,8 @@ class Decoder(torch.nn.Module):
         cfg = self.cfg
         from .runtime import default_context
         ctx = DynamicLinear.context or default_context(self.device)
-        ctx.reserve(max_tokens or batch * max_len, max(s[0] for s in cfg.linear_shapes()),
-                    max(s[1] for s in cfg.linear_shapes()))
+        shapes = self.linear_shapes()
+        ctx.reserve(max_tokens or batch * max_len, max(s[0] for s in shapes), max(s[1] for s in shapes))
         shape = (len(self.model.layers), 2, batch, cfg.n_kv_heads, max_len, cfg.head_dim)
         self.kv = torch.zeros(shape, dtype=torch.float16, device=self.device)
         self.max_len = max_len
@@ -169,50 +191,76 @@ class Decoder(torch.nn.Module):
         self.graph = None
 
     # ---- layers -----------------------------------------------------------------------------
+    def _norm(self, mod, x):
+        if self.glue == 'cuda':
+            return ops.rms_norm(x, mod.weight, mod.eps)
+        return mod(x)
+
+    def _qkv(self, a, h):
+        cfg = self.cfg
+        if self.fuse:
+            return a.qkv_proj(h)
+        return torch.cat((a.q_proj(h), a.k_proj(h), a.v_proj(h)), dim=-1)
+
     def _layer(self, li, layer, x, pos0, decode):
         cfg = self.cfg
         b, s, _ = x.shape
-        h = layer.input_layernorm(x)
+        nh, nkv, d = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         a = layer.self_attn
-        q = a.q_proj(h).view(b, s, cfg.n_heads, cfg.head_dim)
-        k = a.k_proj(h).view(b, s, cfg.n_kv_heads, cfg.head_dim)
-        v = a.v_proj(h).view(b, s, cfg.n_kv_heads, cfg.head_dim)
-        if decode:
-            cos, sin = self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos)
-        else:
-            cos, sin = self.cos[pos0:pos0 + s], self.sin[pos0:pos0 + s]
-        q = _apply_rope(q, cos, sin).transpose(1, 2)
-        k = _apply_rope(k, cos, sin).transpose(1, 2)
-        v = v.transpose(1, 2)
+        h = self._norm(layer.input_layernorm, x)
+        qkv = self._qkv(a, h)                                        # [B, S, (H + 2 Hkv) D]
         kc, vc = self.kv[li, 0], self.kv[li, 1]
+        if self.glue == 'cuda':
+            q = torch.empty((b, nh, s, d), dtype=torch.float16, device=x.device)
+            ops.rope_kv(qkv, self.cos, self.sin, q, kc, vc, b, s, nh, nkv, d,
+                        pos_dev=self.pos if decode else None, pos0=pos0)
+        else:
+            qh, kh, vh = qkv.split((nh * d, nkv * d, nkv * d), dim=-1)
+            if decode:
+                cos, sin = self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos)
+            else:
+                cos, sin = self.cos[pos0:pos0 + s], self.sin[pos0:pos0 + s]
+            q = _apply_rope(qh.reshape(b, s, nh, d), cos, sin).transpose(1, 2)
+            k = _apply_rope(kh.reshape(b, s, nkv, d), cos, sin).transpose(1, 2)
+            v = vh.reshape(b, s, nkv, d).transpose(1, 2)
+            if decode:
+                idx = self.pos.view(1, 1, 1, 1).expand(b, nkv, 1, d)
+                kc.scatter_(2, idx, k)
+                vc.scatter_(2, idx, v)
+            else:
+                kc[:, :, pos0:pos0 + s] = k
+                vc[:, :, pos0:pos0 + s] = v
         if decode:
-            idx = self.pos.view(1, 1, 1, 1).expand(b, cfg.n_kv_heads, 1, cfg.head_dim)
-            kc.scatter_(2, idx, k)
-            vc.scatter_(2, idx, v)
             o = F.scaled_dot_product_attention(q, kc, vc, attn_mask=self.mask, enable_gqa=True)
         else:
-            kc[:, :, pos0:pos0 + s] = k
-            vc[:, :, pos0:pos0 + s] = v
-            o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
-        o = o.transpose(1, 2).reshape(b, s, cfg.n_heads * cfg.head_dim)
+            o = F.scaled_dot_product_attention(q, kc[:, :, pos0:pos0 + s], vc[:, :, pos0:pos0 + s], is_causal=True,
+                                               enable_gqa=True)
+        o = o.transpose(1, 2).reshape(b, s, nh * d)
         x = x + a.o_proj(o)
-        h = layer.post_attention_layernorm(x)
+        h = self._norm(layer.post_attention_layernorm, x)
         m = layer.mlp
-        x = x + m.down_proj(F.silu(m.gate_proj(h)) * m.up_proj(h))
+        if self.fuse:
+            gu = m.gate_up_proj(h)
+            act = ops.silu_mul(gu) if self.glue == 'cuda' else F.silu(gu[..., :cfg.inter]) * gu[..., cfg.inter:]
+        else:
+            act = F.silu(m.gate_proj(h)) * m.up_proj(h)
+        x = x + m.down_proj(act)
         return x
 
     @torch.no_grad()
-    def prefill(self, tokens):
+    def prefill(self, tokens, return_logits=False):
         """tokens [B, S] -> next token ids [B, 1]; fills the KV cache for positions 0..S-1."""
         b, s = tokens.shape
         x = self.embed[tokens]
         for li, layer in enumerate(self.model.layers):
             x = self._layer(li, layer, x, 0, False)
-        last = self.norm(x[:, -1:, :])
+        last = self._norm(self.norm, x[:, -1:, :].contiguous())
         logits = last.reshape(b, -1) @ self.lm_head.t()
         self.mask.fill_(float('-inf'))
         self.mask[..., :s] = 0
         self.pos.fill_(s)
+        if return_logits:
+            return logits
         return logits.argmax(dim=-1, keepdim=True)
 
     def _decode_body(self):
@@ -220,8 +268,8 @@ class Decoder(torch.nn.Module):
         self.mask.index_fill_(3, self.pos, 0.0)
         for li, layer in enumerate(self.model.layers):
             x = self._layer(li, layer, x, 0, True)
-        logits = self.norm(x).reshape(x.shape[0], -1) @ self.lm_head.t()
-        self.next_tok.copy_(logits.argmax(dim=-1, keepdim=True))
+        self.logits = self._norm(self.norm, x).reshape(x.shape[0], -1) @ self.lm_head.t()
+        self.next_tok.copy_(self.logits.argmax(dim=-1, keepdim=True))
         self.pos.add_(1)
 
     @torch.no_grad()
@@ -287,10 +335,10 @@ def measure_ttft_tpot(model, batch, prompt_len=1024, new_tokens=512, warmup=2, t
             'tpot_ms': 1e3 * tpot, 'tokens_per_s': batch * new_tokens / (ttft + (new_tokens - 1) * tpot)}
 
 
-def build_lut(cfg, device='cuda', m_grid=None, cache='warm', n=20):
-    """Profile the decoder's linear shapes on the device and install the LUT on DynamicLinear."""
+def build_lut(shapes, device='cuda', m_grid=None, cache='warm', n=20):
+    """Profile the given (N, K) linear shapes on the device and install the LUT on DynamicLinear."""
     grid = m_grid or [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192, 16384, 32768]
-    prof = Profiler(cfg.linear_shapes(), m_grid=grid, n=n, warmup=3, cache=cache)
+    prof = Profiler(list(shapes), m_grid=grid, n=n, warmup=3, cache=cache)
     prof.profiling(device=device)
     DynamicLinear.prof = prof
     return prof

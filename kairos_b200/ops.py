@@ -151,3 +151,37 @@ def w8a16_gemm(x, w8, wscales, bias=None):
                                     _chk(wscales, torch.float16, 'wscales'), _bias_ptr(bias), out.data_ptr(), m, n, k,
                                     ws.data_ptr(), ws.numel(), stream_ptr()), 'w8a16_gemm')
     return out
+
+
+# ---- element-wise operators around the linears ------------------------------------------------
+def rms_norm(x, weight, eps):
+    """RMSNorm over the last dimension of a contiguous fp16 tensor (fp32 arithmetic, one pass)."""
+    k = x.shape[-1]
+    m = x.numel() // k
+    out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(lib.kairos_rms_norm(_chk(x, torch.float16, 'x'), _chk(weight, torch.float16, 'weight'), out.data_ptr(),
+                                  m, k, float(eps), stream_ptr()), 'rms_norm')
+    return out
+
+
+def silu_mul(gate_up):
+    """silu(gate) * up for the fused activation [..., 2I] -> [..., I]."""
+    i2 = gate_up.shape[-1]
+    m = gate_up.numel() // i2
+    out = torch.empty(gate_up.shape[:-1] + (i2 // 2,), dtype=torch.float16, device=gate_up.device)
+    with torch.cuda.device(gate_up.device):
+        check(lib.kairos_silu_mul(_chk(gate_up, torch.float16, 'gate_up'), out.data_ptr(), m, i2 // 2, stream_ptr()),
+              'silu_mul')
+    return out
+
+
+def rope_kv(qkv, cos, sin, q_out, k_cache, v_cache, b, s, h, hkv, d, pos_dev=None, pos0=0):
+    """Rotary embedding of q / k and the KV-cache write for a fused QKV activation (see the header)."""
+    with torch.cuda.device(qkv.device):
+        check(lib.kairos_rope_kv(_chk(qkv, torch.float16, 'qkv'), _chk(cos, torch.float16, 'cos'),
+                                 _chk(sin, torch.float16, 'sin'), None if pos_dev is None else pos_dev.data_ptr(),
+                                 int(pos0), _chk(q_out, torch.float16, 'q_out'), _chk(k_cache, torch.float16, 'k_cache'),
+                                 _chk(v_cache, torch.float16, 'v_cache'), b, s, h, hkv, d, k_cache.shape[2],
+                                 stream_ptr()), 'rope_kv')
+    return q_out
