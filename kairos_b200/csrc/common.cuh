@@ -113,6 +113,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Same test, but the hardware may park the thread for up to `ns` nanoseconds (it is woken when the phase
+// completes): a waiting warp then does not burn issue slots that working warps need.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 
 // Bounded wait.  Returns false when the limit ran out or another role of this CTA
 // already gave up (`*abort_flag` != 0); the caller then leaves its loop and goes to
@@ -124,8 +137,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
+        for (int i = 0; i < 16; ++i)
+            if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > kWaitCycles) {
             *abort_flag = 1;

@@ -40,7 +40,7 @@ constexpr int kDecFBytes = kDecGroups * kDecRows * 2;                    // 512 
 template <int NT>
 struct DecCfg {
     static constexpr int kXRows = 8 * NT;
-    static constexpr int kXBytes = kXRows * kDecPanelK * 2;              // [tokens][32 chunks][64 B], 64B-swizzled
+    static constexpr int kXBytes = kXRows * kDecPanelK * 2;              // [tokens][16 k blocks][128 B], 128B-swizzled
     static constexpr int kStageBytes = kDecWBytes + kXBytes + 2 * kDecFBytes;
     static constexpr int kStages = NT == 1 ? 5 : 3;
     // consumer sets take alternate panels: more warps per scheduler hide the unpack -> MMA -> scale chain
@@ -60,6 +60,7 @@ struct DecParams {
     int units;      // 32-row units
     int panels;     // 1024-k panels per unit
     int* status;
+    int x_bytes;    // bytes one activation copy brings: token rows of the box x 2048
 };
 
 __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -123,8 +124,8 @@ __global__ void __launch_bounds__(DecCfg<NT>::kThreads, 1)
                     if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* st = stage_base + s * Cfg::kStageBytes;
                     mbar_arrive_expect_tx(&full[s], kDecWBytes + kDecFBytes);
-                    // qweight [N/4][k blocks][128 B]: 16 k blocks (1024 k) of 8 rows
-                    tma_load_3d(st, &tmap_w, &full[s], 0, pn * (kDecPanelK / 64), unit * (kDecRows / kInterleave));
+                    // qweight as 64-bit elements [N/4, K/4]: 8 rows of 256 elements (1024 k): eight 2 KB lines
+                    tma_load_2d(st, &tmap_w, &full[s], pn * 256, unit * (kDecRows / kInterleave));
                     tma_load_2d(st + kDecWBytes + Cfg::kXBytes, &tmap_s, &full[s], unit * kDecRows, pn * kDecGroups);
                     if (++s == kStages) { s = 0; phase ^= 1; }
                 }
@@ -140,9 +141,9 @@ __global__ void __launch_bounds__(DecCfg<NT>::kThreads, 1)
                 for (int pn = 0; pn < p.panels; ++pn) {
                     if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* st = stage_base + s * Cfg::kStageBytes;
-                    mbar_arrive_expect_tx(&full[s], Cfg::kXBytes + kDecFBytes);
-                    // X as [M][K/32][32 halves]: 32 chunks of 64 bytes for every token row
-                    tma_load_3d(st + kDecWBytes, &tmap_x, &full[s], 0, pn * 32, 0);
+                    mbar_arrive_expect_tx(&full[s], p.x_bytes + kDecFBytes);
+                    // X as [M][K/64][64 halves]: 16 lines of 128 bytes for every token row of the box
+                    tma_load_3d(st + kDecWBytes, &tmap_x, &full[s], 0, pn * (kDecPanelK / 64), 0);
                     tma_load_2d(st + kDecWBytes + Cfg::kXBytes + kDecFBytes, &tmap_z, &full[s], unit * kDecRows,
                                 pn * kDecGroups);
                     if (++s == kStages) { s = 0; phase ^= 1; }
@@ -156,8 +157,8 @@ __global__ void __launch_bounds__(DecCfg<NT>::kThreads, 1)
         const int grp = warp % kDecSetWarps;
         const int set = warp / kDecSetWarps;
         const uint32_t ones = 0x3c003c00u;           // half2(1, 1)
-        // packed chunk of (row r, this group): qweight row r >> 2, k block k0 = 2 grp + (t >> 1), 16-byte
-        // unit 2 (r & 3) + (t & 1) of its 128-byte line, XOR-swizzled by k0 & 7 (128-byte swizzle)
+        // packed chunk of (row r, this group): qweight row r >> 2 (2048 bytes per panel), k block
+        // k0 = 2 grp + (t >> 1), 16-byte unit 2 (r & 3) + (t & 1) of its 128-byte line
         const int k0 = 2 * grp + (t >> 1);
         uint32_t w_off[2][2];
 #pragma unroll
@@ -165,19 +166,17 @@ __global__ void __launch_bounds__(DecCfg<NT>::kThreads, 1)
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int r = 16 * rb + g + 8 * h;
-                w_off[rb][h] = (uint32_t)((r >> 2) * (kDecPanelK * 2) + k0 * 128 +
-                                          (((2 * (r & 3) + (t & 1)) ^ (k0 & 7)) << 4));
+                w_off[rb][h] = (uint32_t)((r >> 2) * (kDecPanelK * 2) + k0 * 128 + ((2 * (r & 3) + (t & 1)) << 4));
             }
-        // activations of token g (+ 8 nt): chunk 4 grp + t (64 bytes); the 16-byte units are XOR-swizzled by
-        // bits 7-8 of the offset (64-byte swizzle)
+        // activations of token g (+ 8 nt): the half (t & 1) of the 128-byte line of k block k0; the 16-byte
+        // units of a line are XOR-swizzled by k0 & 7 (128-byte swizzle of the tensor map)
         uint32_t x_off[NT][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const uint32_t base = (uint32_t)((g + 8 * nt) * (kDecPanelK * 2) + (4 * grp + t) * 64);
-            const uint32_t sw = (base >> 7) & 3u;
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int b = 0; b < 4; ++b) x_off[nt][b] = kDecWBytes + base + ((b ^ sw) << 4);
-        }
+            for (int b = 0; b < 4; ++b)
+                x_off[nt][b] = (uint32_t)(kDecWBytes + (g + 8 * nt) * (kDecPanelK * 2) + k0 * 128 +
+                                          (((4 * (t & 1) + b) ^ (k0 & 7)) << 4));
         int s = 0, it = 0;
         uint32_t phase = 0, panel_no = 0;
         bool ok = true;
@@ -310,17 +309,20 @@ static int launch_decode(const void* X, const void* qweight, const void* scales,
     using Cfg = DecCfg<NT>;
     CUtensorMap tw, tx, ts, tz;
     int rc;
-    {   // qweight int16 [N/4, K] viewed as [N/4][K/64 k blocks][64]: 128-byte lines, 128-byte swizzle
-        const uint64_t dims[3] = {64, (uint64_t)K / 64, (uint64_t)N / 4}, strides[2] = {128, (uint64_t)K * 2};
-        const uint32_t box[3] = {64, kDecPanelK / 64, kDecRows / kInterleave};
-        if ((rc = make_tmap(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, qweight, dims, strides, box,
-                            CU_TENSOR_MAP_SWIZZLE_128B)) != KAIROS_OK) return rc;
+    {   // qweight int16 [N/4, K] viewed as 64-bit elements [N/4, K/4]: long lines keep the copy engine efficient
+        const uint64_t dims[2] = {(uint64_t)K / 4, (uint64_t)N / 4}, strides[1] = {(uint64_t)K * 2};
+        const uint32_t box[2] = {256, kDecRows / kInterleave};
+        if ((rc = make_tmap(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, qweight, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_NONE)) != KAIROS_OK) return rc;
     }
-    {   // X fp16 [M, K] viewed as [M][K/32][32]
-        const uint64_t dims[3] = {32, (uint64_t)K / 32, (uint64_t)M}, strides[2] = {64, (uint64_t)K * 2};
-        const uint32_t box[3] = {32, 32, (uint32_t)Cfg::kXRows};
+    // only the token rows that exist are copied (power of two >= M)
+    int x_rows = 1;
+    while (x_rows < M) x_rows *= 2;
+    {   // X fp16 [M, K] viewed as [M][K/64][64]: 128-byte lines, 128-byte swizzle
+        const uint64_t dims[3] = {64, (uint64_t)K / 64, (uint64_t)M}, strides[2] = {128, (uint64_t)K * 2};
+        const uint32_t box[3] = {64, kDecPanelK / 64, (uint32_t)x_rows};
         if ((rc = make_tmap(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, X, dims, strides, box,
-                            CU_TENSOR_MAP_SWIZZLE_64B)) != KAIROS_OK) return rc;
+                            CU_TENSOR_MAP_SWIZZLE_128B)) != KAIROS_OK) return rc;
     }
     {   // factors fp16 [K/128, N]
         const uint64_t dims[2] = {(uint64_t)N, (uint64_t)K / kGroup}, strides[1] = {(uint64_t)N * 2};
@@ -337,6 +339,7 @@ static int launch_decode(const void* X, const void* qweight, const void* scales,
     p.units = (N + kDecRows - 1) / kDecRows;
     p.panels = (K + kDecPanelK - 1) / kDecPanelK;
     p.status = device_status_word();
+    p.x_bytes = x_rows * kDecPanelK * 2;
     if (!p.status) return KAIROS_ERR_CUDA;
     static bool attr_set = false;
     if (!attr_set) {

@@ -1,0 +1,316 @@
+// Large-M GEMMs on CTA pairs: Y[M,N] = X . W^T with both operands staged by TMA (W8A8 kind::i8 and FP16
+// kind::f16), one 256 (weight rows) x 256 (tokens) tile per cluster of two CTAs.
+//
+// Why pairs: with one CTA per 128 x 256 tile the int8 MMA drains its shared-memory operands (48 KB per
+// 128-byte k block) faster than one SM's shared memory can deliver them (tensor pipe 50 % active).  With
+// tcgen05.mma.cta_group::2 each CTA stages its own 128 weight rows and only HALF of the token tile
+// (32 KB per k block), the pair's tensor cores share the operands, and each CTA keeps its 128 x 256
+// accumulator in its own TMEM.
+//
+// Protocol (no multicast anywhere):
+//   * both CTAs issue plain TMA loads into their own shared memory; the loads of both signal the FULL
+//     barrier of the leader (rank 0), which its producers armed with the byte count of both CTAs;
+//   * the leader's MMA thread issues the pair-wide MMAs and commits twice per stage: once to its own
+//     EMPTY barrier, once to the peer's (address mapped into the cluster window), same for the
+//     accumulator-ready barriers;
+//   * the peer's epilogue warps release the accumulator buffer by remote arrives on the leader's barrier.
+// Every mbarrier wait is bounded (status word on timeout); the two cluster-wide barriers at start and end
+// are reached by every thread on every path.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace kairos {
+
+int make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle);   // tensormap.cu
+int device_sm_count();        // gemm_sm100.cu
+int* device_status_word();    // api.cu
+
+constexpr int kP2Rows = 128;                       // weight rows per CTA (256 per pair)
+constexpr int kP2Tokens = 256;                     // tokens per tile (128 staged by each CTA)
+constexpr int kP2StageBytes = 2 * kP2Rows * 128;   // A tile + half of the token tile, one 128-byte k block
+constexpr int kP2Stages = 6;
+constexpr int kP2Threads = 32 * 7;
+constexpr int kP2SmemBytes = kP2Stages * kP2StageBytes + 8 * (2 * kP2Stages + 4) + 64 + 1024;
+
+struct Pair2Params {
+    int M, N, K;
+    int n_tiles, m_tiles, kb_total;
+    const __half* s1;
+    const __half* sx;
+    const __half* bias;
+    __half* Y;
+    int32_t* acc_dbg;
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t peer_addr(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load of a CTA of a pair: data into this CTA's shared memory, completion on `bar_cluster_addr`
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const void* tmap, uint32_t bar_cluster_addr, int c0, int c1,
+                                                 int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, "
+        "%5}], [%2];" ::"r"(smem_u32(dst)),
+        "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+                 : "memory");
+}
+template <bool kInt8>
+__device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    if constexpr (kInt8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+template <bool kInt8>
+__global__ void __launch_bounds__(kP2Threads, 1)
+    umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                          const Pair2Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kP2Stages * kP2StageBytes);   // used in the leader only
+    uint64_t* empty = full + kP2Stages;                                                // one set per CTA
+    uint64_t* tmem_full = empty + kP2Stages;                                           // [2], per CTA
+    uint64_t* tmem_empty = tmem_full + 2;                                              // [2], leader only
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+    // pair-wide instruction: M = 256 (128 rows per CTA), N = 256
+    constexpr uint32_t kIdesc = (kInt8 ? (2u << 4) | (1u << 7) | (1u << 10) : (1u << 4)) |
+                                ((uint32_t)(kP2Tokens >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kP2Stages; ++s) {
+            mbar_init(&full[s], 2);              // the leader's two producers (they arm both CTAs' bytes)
+            mbar_init(&empty[s], 1);             // one commit of the leader's MMA thread
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 8);        // four epilogue warps of each CTA
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                          // the peer's barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
+    const int total_tiles = p.n_tiles * p.m_tiles;
+
+    if (warp == 0 || warp == 6) {
+        // ---------------- producers (both CTAs): warp 0 = weights, warp 6 = activations ----------------
+        if (lane == 0) {
+            const bool is_w = warp == 0;
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
+                const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+                const int row0 = is_w ? n_tile * 256 + (int)rank * kP2Rows : m_tile * kP2Tokens + (int)rank * 128;
+                for (int kb = 0; kb < p.kb_total; ++kb) {
+                    if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* st = smem + s * kP2StageBytes + (is_w ? 0 : kP2Rows * 128);
+                    if (leader) mbar_arrive_expect_tx(&full[s], 2 * kP2Rows * 128);   // this CTA's bytes + the peer's
+                    tma_load_3d_pair(st, is_w ? (const void*)&tmap_w : (const void*)&tmap_x,
+                                     peer_addr(smem_u32(&full[s]), 0), 0, row0, kb);
+                    if (++s == kP2Stages) { s = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader only) ----------------
+        if (leader && lane == 0) {
+            int s = 0, it = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++it) {
+                const int b = it & 1;
+                if (!mbar_wait(&tmem_empty[b], ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * kP2Tokens);
+                for (int kb = 0; kb < p.kb_total; ++kb) {
+                    if (!mbar_wait(&full[s], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    uint8_t* st = smem + s * kP2StageBytes;
+                    const uint64_t adesc = umma_desc_sw128(smem_u32(st));
+                    const uint64_t bdesc = umma_desc_sw128(smem_u32(st + kP2Rows * 128));
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        umma_pair<kInt8>(d_tmem, adesc + 2 * j, bdesc + 2 * j, kIdesc, (kb > 0 || j > 0) ? 1u : 0u);
+                    umma_commit_pair(smem_u32(&empty[s]));                    // this CTA's stage is free
+                    umma_commit_pair(peer_addr(smem_u32(&empty[s]), 1));      // and the peer's
+                    if (++s == kP2Stages) { s = 0; phase ^= 1; }
+                }
+                if (ok) {
+                    umma_commit_pair(smem_u32(&tmem_full[b]));
+                    umma_commit_pair(peer_addr(smem_u32(&tmem_full[b]), 1));
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        int it = 0;
+        bool ok = true;
+        for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++it) {
+            const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+            const int n = n_tile * 256 + (int)rank * kP2Rows + row;
+            const bool n_ok = n < p.N;
+            const int b = it & 1;
+            float s1f = 0.f;
+            if constexpr (kInt8) s1f = n_ok ? __half2float(__ldg(p.s1 + n)) : 0.f;
+            const bool has_bias = p.bias != nullptr;
+            const __half bias_n = (has_bias && n_ok) ? __ldg(p.bias + n) : __float2half_rn(0.f);
+            if (!mbar_wait(&tmem_full[b], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kP2Tokens);
+#pragma unroll 1
+            for (int c0 = 0; c0 < kP2Tokens; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const int m = m_tile * kP2Tokens + c0 + c;
+                    if (!n_ok || m >= p.M) continue;
+                    __half y;
+                    if constexpr (kInt8) {
+                        // half(float(acc) * (float(s1[n]) * float(sx[m])))
+                        const float sc = __fmul_rn(s1f, __half2float(__ldg(p.sx + m)));
+                        y = __float2half_rn(__fmul_rn((float)(int32_t)r[c], sc));
+                        if (p.acc_dbg) p.acc_dbg[(size_t)m * p.N + n] = (int32_t)r[c];
+                    } else {
+                        y = __float2half_rn(__uint_as_float(r[c]));
+                    }
+                    if (has_bias) y = __hadd(y, bias_n);
+                    p.Y[(size_t)m * p.N + n] = y;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(peer_addr(smem_u32(&tmem_empty[b]), 0));   // the leader's barrier
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, KAIROS_ERR_DEVICE);
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    cluster_sync_all();                          // nobody signals a CTA that has already left
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// Returns KAIROS_OK after launching, or 1 when the problem does not suit CTA pairs (caller falls back to
+// the one-CTA kernel).
+template <bool kInt8>
+int launch_gemm_pair(const void* X, const void* W, const __half* s1, const __half* sx, const __half* bias, void* Y,
+                     void* acc_dbg, int M, int N, int K, cudaStream_t stream) {
+    const int sms = device_sm_count();
+    const int n_tiles = (N + 255) / 256, m_tiles = (M + kP2Tokens - 1) / kP2Tokens;
+    if (M < 512 || n_tiles * m_tiles < sms / 2) return 1;
+    const uint64_t es = kInt8 ? 1 : 2, bk = kInt8 ? 128 : 64;
+    CUtensorMap tw, tx;
+    int rc;
+    {
+        const uint64_t dims[3] = {bk, (uint64_t)N, (uint64_t)K / bk}, strides[2] = {(uint64_t)K * es, 128};
+        const uint32_t box[3] = {(uint32_t)bk, kP2Rows, 1};
+        if ((rc = make_tmap(&tw, kInt8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, W, dims,
+                            strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != KAIROS_OK) return rc;
+    }
+    {
+        const uint64_t dims[3] = {bk, (uint64_t)M, (uint64_t)K / bk}, strides[2] = {(uint64_t)K * es, 128};
+        const uint32_t box[3] = {(uint32_t)bk, 128, 1};
+        if ((rc = make_tmap(&tx, kInt8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, X, dims,
+                            strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != KAIROS_OK) return rc;
+    }
+    Pair2Params p;
+    p.M = M; p.N = N; p.K = K;
+    p.n_tiles = n_tiles; p.m_tiles = m_tiles; p.kb_total = K / (int)bk;
+    p.s1 = s1; p.sx = sx; p.bias = bias;
+    p.Y = static_cast<__half*>(Y);
+    p.acc_dbg = static_cast<int32_t*>(acc_dbg);
+    p.status = device_status_word();
+    if (!p.status) return KAIROS_ERR_CUDA;
+    static bool attr_set = false;
+    if (!attr_set) {
+        KAIROS_CUDA_OK(cudaFuncSetAttribute(umma_gemm_pair_kernel<kInt8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            kP2SmemBytes));
+        attr_set = true;
+    }
+    int clusters = n_tiles * m_tiles;
+    if (clusters > sms / 2) clusters = sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * clusters));
+    cfg.blockDim = dim3(kP2Threads);
+    cfg.dynamicSmemBytes = kP2SmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, umma_gemm_pair_kernel<kInt8>, tw, tx, p);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    return launch_status();
+}
+
+template int launch_gemm_pair<true>(const void*, const void*, const __half*, const __half*, const __half*, void*, void*,
+                                    int, int, int, cudaStream_t);
+template int launch_gemm_pair<false>(const void*, const void*, const __half*, const __half*, const __half*, void*,
+                                     void*, int, int, int, cudaStream_t);
+
+}  // namespace kairos

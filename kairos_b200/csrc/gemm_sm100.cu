@@ -24,6 +24,7 @@
 // Every mbarrier wait is bounded; on a timeout the CTA raises a status word and drains.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -638,6 +639,18 @@ static int launch_one(const GemmArgs& a, const Plan& pl) {
     return launch_status();
 }
 
+template <bool kInt8>
+int launch_gemm_pair(const void* X, const void* W, const __half* s1, const __half* sx, const __half* bias, void* Y,
+                     void* acc_dbg, int M, int N, int K, cudaStream_t stream);   // gemm2_sm100.cu
+
+static bool pairs_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("KAIROS_NO_PAIR");
+        return !(v && v[0] == '1');
+    }();
+    return on;
+}
+
 template <bool kInt8, int kMode>
 int launch_gemm(const GemmArgs& a) {
     if (a.M < 0 || a.N <= 0 || a.K <= 0 || (a.K % kGroup) != 0 || (a.N % kInterleave) != 0) return KAIROS_ERR_SHAPE;
@@ -645,6 +658,13 @@ int launch_gemm(const GemmArgs& a) {
     if (!a.X || !a.W || !a.Y || ((uintptr_t)a.X & 15) || ((uintptr_t)a.W & 15) || ((uintptr_t)a.Y & 1))
         return KAIROS_ERR_ALIGN;
     if (kMode == kModeW4 && (a.N % 8) != 0) return KAIROS_ERR_SHAPE;   // factor rows must be 16-byte multiples
+    if constexpr (kMode == kModeTma) {
+        // large problems run on CTA pairs (256 x 256 tiles); 1 = not suitable, use the one-CTA kernel
+        if (pairs_enabled()) {
+            const int rc = launch_gemm_pair<kInt8>(a.X, a.W, a.s1, a.sx, a.bias, a.Y, a.acc_dbg, a.M, a.N, a.K, a.stream);
+            if (rc != 1) return rc;
+        }
+    }
     const Plan pl = make_plan(a.M, a.N, a.K, kInt8);
     if (pl.partial_bytes > 0 && (!a.workspace || ((uintptr_t)a.workspace & 15) || a.workspace_bytes < pl.partial_bytes))
         return KAIROS_ERR_WORKSPACE;
