@@ -153,6 +153,14 @@ int kairos_rms_norm(const void* X_f16, const void* W_f16, void* Y_f16, int M, in
                     kairos_stream_t stream);
 /* Y[m,i] = silu(GU[m,i]) * GU[m,I+i] for the fused gate|up activation GU [M, 2I]; I % 8 == 0 */
 int kairos_silu_mul(const void* GU_f16, void* Y_f16, int M, int I, kairos_stream_t stream);
+/* The same two operators emitting the precision a following W8A8 linear consumes: per-token int8 Xq + fp16
+ * scale sx, bit-identical to kairos_act_quant_i8 applied to the fp16 result; the fp16 tensor itself is
+ * written only when Y is given.  K % 16 == 0, K <= 16384; I % 16 == 0, I <= 32768. */
+int kairos_rms_norm_quant(const void* X_f16, const void* W_f16, void* Y_f16_or_null, void* Xq_i8, void* sx_f16,
+                          int M, int K, float eps, kairos_stream_t stream);
+int kairos_silu_mul_quant(const void* GU_f16, void* Y_f16_or_null, void* Xq_i8, void* sx_f16, int M, int I,
+                          kairos_stream_t stream);
+
 /* Rotary embedding (rotate-half) of the q and k heads of a fused QKV activation [B*S, (H+2Hkv)*D] plus the
  * KV-cache write: Q_out [B,H,S,D], caches [B,Hkv,max_len,D]; token (b,s) is at position pos0 + s where
  * pos0 = *pos_dev (int64 in device memory, for graph-replayed decode steps) or the host value. */
@@ -201,6 +209,10 @@ void kairos_layer_destroy(kairos_layer* layer);
  * for ids 2, 3, 5 and only on a cache miss. */
 int kairos_switched_linear(kairos_layer* layer, const void* X_f16, void* Y_f16, int M, int comp_type,
                            kairos_stream_t stream);
+/* Kernel id 2 for activations that arrive already quantized (by the operators above): conversion on a
+ * cache miss, then the W8A8 GEMM; no activation pass. */
+int kairos_switched_linear_q8(kairos_layer* layer, const void* Xq_i8, const void* sx_f16, void* Y_f16, int M,
+                              kairos_stream_t stream);
 /* Convert ahead of use (e.g. on a side stream, one layer ahead): fills the cache entry the
  * given kernel id needs and returns; a later kairos_switched_linear on any stream waits for it. */
 int kairos_layer_prefetch(kairos_layer* layer, int comp_type, kairos_stream_t stream);

@@ -418,6 +418,22 @@ int kairos_switched_linear(kairos_layer* layer, const void* X, void* Y, int M, i
     return kairos::run_switched(L, X, Y, M, comp_type, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int kairos_switched_linear_q8(kairos_layer* layer, const void* Xq, const void* sx, void* Y, int M,
+                              kairos_stream_t stream) {
+    if (!layer) return KAIROS_ERR_ARG;
+    if (M < 0) return KAIROS_ERR_SHAPE;
+    if (M == 0) return KAIROS_OK;
+    Layer* L = reinterpret_cast<Layer*>(layer);
+    std::lock_guard<std::mutex> lk(L->ctx->mu);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const void* w8 = nullptr;
+    int rc;
+    if ((rc = kairos::converted_weight(L, 8, st, &w8)) != KAIROS_OK) return rc;
+    if ((rc = kairos::ensure_gemm_ws(L->ctx, M, L->N, L->K, st)) != KAIROS_OK) return rc;
+    return kairos_w8a8_gemm(Xq, w8, L->scales_1, sx, L->bias, Y, nullptr, M, L->N, L->K, L->ctx->gemm_ws,
+                            L->ctx->gemm_bytes, stream);
+}
+
 int kairos_layer_prefetch(kairos_layer* layer, int comp_type, kairos_stream_t stream) {
     if (!layer) return KAIROS_ERR_ARG;
     Layer* L = reinterpret_cast<Layer*>(layer);

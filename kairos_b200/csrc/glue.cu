@@ -82,6 +82,154 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* __restrict_
     reinterpret_cast<uint4*>(Y + (size_t)m * I)[c] = o4;
 }
 
+// Block-wide max of a non-negative value (256 threads), result in every thread.
+__device__ __forceinline__ float block_max_256(float v, float* scratch8) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();                       // scratch may still be read from a previous reduction
+    if ((threadIdx.x & 31) == 0) scratch8[threadIdx.x >> 5] = v;
+    __syncthreads();
+    v = scratch8[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) v = fmaxf(v, scratch8[w]);
+    return v;
+}
+
+// Per-token symmetric int8 quantization of 8 fp16 values held in a uint4, with the arithmetic of
+// act_quant_kernel (IEEE division, round-half-even): bit-identical to quantizing the stored fp16 tensor.
+__device__ __forceinline__ uint2 quant8(const uint4& v, float scale) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    uint32_t w[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const float2 f0 = __half22float2(h[2 * j]), f1 = __half22float2(h[2 * j + 1]);
+        const int q0 = __float2int_rn(__fdiv_rn(f0.x, scale)), q1 = __float2int_rn(__fdiv_rn(f0.y, scale));
+        const int q2 = __float2int_rn(__fdiv_rn(f1.x, scale)), q3 = __float2int_rn(__fdiv_rn(f1.y, scale));
+        w[j] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+               ((uint32_t)(q3 & 0xff) << 24);
+    }
+    return make_uint2(w[0], w[1]);
+}
+
+__device__ __forceinline__ float absmax8(const uint4& v) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+    return m;
+}
+
+// RMSNorm that hands its result to a W8A8 linear in the precision that kernel consumes: the fp16 result is
+// formed in registers, quantized per token to int8 (+ fp16 scale) and written ONCE as int8; the fp16 tensor
+// is written only when a consumer needs it (Y != null).  Output equals act_quant(rms_norm(X)) bit for bit.
+template <int R>
+__global__ void __launch_bounds__(256) rms_norm_quant_kernel(const __half* __restrict__ X, const __half* __restrict__ W,
+                                                             __half* __restrict__ Y, int8_t* __restrict__ Xq,
+                                                             __half* __restrict__ sx, int K, float eps) {
+    __shared__ float part[8];
+    const int token = blockIdx.x;
+    const int chunks = K >> 3;
+    const uint4* row = reinterpret_cast<const uint4*>(X + (size_t)token * K);
+    uint4 v[R];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int c = threadIdx.x + r * 256;
+        if (c < chunks) {
+            v[r] = __ldg(row + c);
+            const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                ss += f.x * f.x + f.y * f.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) ss += part[w];
+    const float inv = rsqrtf(ss / (float)K + eps);
+    const uint4* wv = reinterpret_cast<const uint4*>(W);
+    float amax = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int c = threadIdx.x + r * 256;
+        if (c < chunks) {
+            const uint4 wq = __ldg(wv + c);
+            const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+            const __half2* g = reinterpret_cast<const __half2*>(&wq);
+            uint4 o4;
+            __half2* o = reinterpret_cast<__half2*>(&o4);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]), gw = __half22float2(g[i]);
+                o[i] = __floats2half2_rn(f.x * inv * gw.x, f.y * inv * gw.y);
+            }
+            v[r] = o4;                                       // the fp16 result replaces the input
+            amax = fmaxf(amax, absmax8(o4));
+            if (Y) reinterpret_cast<uint4*>(Y + (size_t)token * K)[c] = o4;
+        }
+    }
+    amax = block_max_256(amax, part);
+    const float scale = __fdiv_rn(fmaxf(amax, 1e-7f), 127.0f);
+    if (threadIdx.x == 0) sx[token] = __float2half_rn(scale);
+    uint2* out = reinterpret_cast<uint2*>(Xq + (size_t)token * K);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int c = threadIdx.x + r * 256;
+        if (c < chunks) out[c] = quant8(v[r], scale);
+    }
+}
+
+// SiLU(gate) * up followed by the same per-token int8 quantization, one CTA per token.
+template <int R>
+__global__ void __launch_bounds__(256) silu_mul_quant_kernel(const __half* __restrict__ GU, __half* __restrict__ Y,
+                                                             int8_t* __restrict__ Xq, __half* __restrict__ sx, int I) {
+    __shared__ float part[8];
+    const int token = blockIdx.x;
+    const int chunks = I >> 3;
+    const uint4* gp = reinterpret_cast<const uint4*>(GU + (size_t)token * 2 * I);
+    const uint4* up = reinterpret_cast<const uint4*>(GU + (size_t)token * 2 * I + I);
+    uint4 v[R];
+    float amax = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int c = threadIdx.x + r * 256;
+        if (c < chunks) {
+            const uint4 g4 = __ldg(gp + c), u4 = __ldg(up + c);
+            const __half2* g = reinterpret_cast<const __half2*>(&g4);
+            const __half2* u = reinterpret_cast<const __half2*>(&u4);
+            uint4 o4;
+            __half2* o = reinterpret_cast<__half2*>(&o4);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(g[i]);
+                const __half2 sl = __floats2half2_rn(f.x / (1.f + __expf(-f.x)), f.y / (1.f + __expf(-f.y)));
+                o[i] = __hmul2(sl, u[i]);
+            }
+            v[r] = o4;
+            amax = fmaxf(amax, absmax8(o4));
+            if (Y) reinterpret_cast<uint4*>(Y + (size_t)token * I)[c] = o4;
+        }
+    }
+    amax = block_max_256(amax, part);
+    const float scale = __fdiv_rn(fmaxf(amax, 1e-7f), 127.0f);
+    if (threadIdx.x == 0) sx[token] = __float2half_rn(scale);
+    uint2* out = reinterpret_cast<uint2*>(Xq + (size_t)token * I);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int c = threadIdx.x + r * 256;
+        if (c < chunks) out[c] = quant8(v[r], scale);
+    }
+}
+
 // Rotary embedding (rotate-half convention) of the q and k heads of a fused QKV activation and the
 // KV-cache write, one thread per pair (d, d + D/2) of one head of one token.
 //   QKV  [B*S, (H + 2 Hkv) * D]      Q_out [B, H, S, D]      cache K / V [B, Hkv, max_len, D]
@@ -161,5 +309,46 @@ extern "C" int kairos_rope_kv(const void* QKV, const void* cos_table, const void
         static_cast<const __half*>(QKV), static_cast<const __half*>(cos_table), static_cast<const __half*>(sin_table),
         static_cast<const long long*>(pos_dev_or_null), pos0, static_cast<__half*>(Q_out),
         static_cast<__half*>(K_cache), static_cast<__half*>(V_cache), B, S, H, Hkv, D, max_len);
+    return launch_status();
+}
+
+extern "C" int kairos_rms_norm_quant(const void* X, const void* W, void* Y_or_null, void* Xq, void* sx, int M, int K,
+                                     float eps, kairos_stream_t stream) {
+    using namespace kairos;
+    if (M < 0 || K <= 0 || (K % 16) != 0 || K > 8 * 256 * 8) return KAIROS_ERR_SHAPE;
+    if (M == 0) return KAIROS_OK;
+    if (!X || !W || !Xq || !sx || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)Xq & 15) ||
+        ((uintptr_t)Y_or_null & 15))
+        return KAIROS_ERR_ALIGN;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const __half* x = static_cast<const __half*>(X);
+    const __half* w = static_cast<const __half*>(W);
+    __half* y = static_cast<__half*>(Y_or_null);
+    int8_t* q = static_cast<int8_t*>(Xq);
+    __half* s = static_cast<__half*>(sx);
+    const int per = (K / 8 + 255) / 256;
+    if (per <= 1) rms_norm_quant_kernel<1><<<M, 256, 0, st>>>(x, w, y, q, s, K, eps);
+    else if (per <= 2) rms_norm_quant_kernel<2><<<M, 256, 0, st>>>(x, w, y, q, s, K, eps);
+    else if (per <= 4) rms_norm_quant_kernel<4><<<M, 256, 0, st>>>(x, w, y, q, s, K, eps);
+    else rms_norm_quant_kernel<8><<<M, 256, 0, st>>>(x, w, y, q, s, K, eps);
+    return launch_status();
+}
+
+extern "C" int kairos_silu_mul_quant(const void* GU, void* Y_or_null, void* Xq, void* sx, int M, int I,
+                                     kairos_stream_t stream) {
+    using namespace kairos;
+    if (M < 0 || I <= 0 || (I % 16) != 0 || I > 8 * 256 * 16) return KAIROS_ERR_SHAPE;
+    if (M == 0) return KAIROS_OK;
+    if (!GU || !Xq || !sx || ((uintptr_t)GU & 15) || ((uintptr_t)Xq & 15) || ((uintptr_t)Y_or_null & 15))
+        return KAIROS_ERR_ALIGN;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const __half* gu = static_cast<const __half*>(GU);
+    __half* y = static_cast<__half*>(Y_or_null);
+    int8_t* q = static_cast<int8_t*>(Xq);
+    __half* s = static_cast<__half*>(sx);
+    const int per = (I / 8 + 255) / 256;
+    if (per <= 4) silu_mul_quant_kernel<4><<<M, 256, 0, st>>>(gu, y, q, s, I);
+    else if (per <= 8) silu_mul_quant_kernel<8><<<M, 256, 0, st>>>(gu, y, q, s, I);
+    else silu_mul_quant_kernel<16><<<M, 256, 0, st>>>(gu, y, q, s, I);
     return launch_status();
 }

@@ -167,6 +167,26 @@ class DynamicLinear(torch.nn.Module):
             check(rc, f'DynamicLinear._forward(comp_type={comp_type}, m={m}, shape={self.shape})')
         return out
 
+    def wants_int8(self, m):
+        """True when the LUT sends M = m to the W8A8 kernel: the operator before this layer can then emit
+        int8 activations directly (``ops.rms_norm_quant`` / ``ops.silu_mul_quant``) and call
+        :meth:`forward_q8`, instead of writing fp16 for a separate quantization pass."""
+        if m != self.pre_m:
+            self.pre_m = m
+            self.comp_type = type(self).prof.get_comp_type(self.shape, m)
+        return self.comp_type == COMP_TYPE_NAME['w8a8']
+
+    @torch.no_grad()
+    def forward_q8(self, xq, sx):
+        """W8A8 on activations that are already quantized: xq int8 [..., K], sx fp16 [tokens] -> [..., N]."""
+        m = xq.numel() // self.in_features
+        out = torch.empty(xq.shape[:-1] + (self.out_features,), dtype=torch.float16, device=xq.device)
+        rc = lib.kairos_switched_linear_q8(self._handle or self._native(), xq.data_ptr(), sx.data_ptr(), out.data_ptr(),
+                                           m, _raw_stream(xq.device.index))
+        if rc:
+            check(rc, f'DynamicLinear.forward_q8(m={m}, shape={self.shape})')
+        return out
+
     @torch.no_grad()
     def prefetch(self, comp_type, stream=None):
         """Convert the weight the kernel id needs ahead of time (e.g. on a side stream)."""

@@ -134,6 +134,7 @@ class Decoder(torch.nn.Module):
         self.cfg = cfg
         self.device = torch.device(device)
         self.fuse, self.glue = fuse_linears, glue
+        self.fuse_quant = True       # let RMSNorm / SiLU*up emit int8 when the next linear runs W8A8
         n_layers = cfg.layers if layers is None else layers
         gen = torch.Generator(device=self.device).manual_seed(seed)
         self.model = _Inner()
@@ -207,8 +208,13 @@ class Decoder(torch.nn.Module):
         b, s, _ = x.shape
         nh, nkv, d = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         a = layer.self_attn
-        h = self._norm(layer.input_layernorm, x)
-        qkv = self._qkv(a, h)                                        # [B, S, (H + 2 Hkv) D]
+        if self.fuse and self.glue == 'cuda' and self.fuse_quant and a.qkv_proj.wants_int8(b * s):
+            # the norm emits the int8 activations the W8A8 kernel consumes; no fp16 round trip
+            xq, sx, _ = ops.rms_norm_quant(x, layer.input_layernorm.weight, layer.input_layernorm.eps)
+            qkv = a.qkv_proj.forward_q8(xq, sx)
+        else:
+            h = self._norm(layer.input_layernorm, x)
+            qkv = self._qkv(a, h)                                    # [B, S, (H + 2 Hkv) D]
         kc, vc = self.kv[li, 0], self.kv[li, 1]
         if self.glue == 'cuda':
             q = torch.empty((b, nh, s, d), dtype=torch.float16, device=x.device)
@@ -237,10 +243,18 @@ class Decoder(torch.nn.Module):
                                                enable_gqa=True)
         o = o.transpose(1, 2).reshape(b, s, nh * d)
         x = x + a.o_proj(o)
-        h = self._norm(layer.post_attention_layernorm, x)
         m = layer.mlp
+        fq = self.fuse and self.glue == 'cuda' and self.fuse_quant
+        if fq and m.gate_up_proj.wants_int8(b * s):
+            xq, sx, _ = ops.rms_norm_quant(x, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
+            gu = m.gate_up_proj.forward_q8(xq, sx)
+        else:
+            h = self._norm(layer.post_attention_layernorm, x)
+            gu = m.gate_up_proj(h) if self.fuse else None
         if self.fuse:
-            gu = m.gate_up_proj(h)
+            if fq and m.down_proj.wants_int8(b * s):
+                aq, sa, _ = ops.silu_mul_quant(gu)
+                return x + m.down_proj.forward_q8(aq, sa)
             act = ops.silu_mul(gu) if self.glue == 'cuda' else F.silu(gu[..., :cfg.inter]) * gu[..., cfg.inter:]
         else:
             act = F.silu(m.gate_proj(h)) * m.up_proj(h)

@@ -185,3 +185,32 @@ def rope_kv(qkv, cos, sin, q_out, k_cache, v_cache, b, s, h, hkv, d, pos_dev=Non
                                  _chk(v_cache, torch.float16, 'v_cache'), b, s, h, hkv, d, k_cache.shape[2],
                                  stream_ptr()), 'rope_kv')
     return q_out
+
+
+def rms_norm_quant(x, weight, eps, want_f16=False):
+    """RMSNorm emitting per-token int8 + fp16 scales (what a W8A8 linear consumes); also the fp16 result
+    when `want_f16`.  Returns (xq, sx, y_or_None)."""
+    k = x.shape[-1]
+    m = x.numel() // k
+    xq = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    sx = torch.empty((m,), dtype=torch.float16, device=x.device)
+    y = torch.empty_like(x) if want_f16 else None
+    with torch.cuda.device(x.device):
+        check(lib.kairos_rms_norm_quant(_chk(x, torch.float16, 'x'), _chk(weight, torch.float16, 'weight'),
+                                        None if y is None else y.data_ptr(), xq.data_ptr(), sx.data_ptr(), m, k,
+                                        float(eps), stream_ptr()), 'rms_norm_quant')
+    return xq, sx, y
+
+
+def silu_mul_quant(gate_up, want_f16=False):
+    """silu(gate) * up emitting per-token int8 + fp16 scales.  Returns (xq, sx, y_or_None)."""
+    i2 = gate_up.shape[-1]
+    m = gate_up.numel() // i2
+    shape = gate_up.shape[:-1] + (i2 // 2,)
+    xq = torch.empty(shape, dtype=torch.int8, device=gate_up.device)
+    sx = torch.empty((m,), dtype=torch.float16, device=gate_up.device)
+    y = torch.empty(shape, dtype=torch.float16, device=gate_up.device) if want_f16 else None
+    with torch.cuda.device(gate_up.device):
+        check(lib.kairos_silu_mul_quant(_chk(gate_up, torch.float16, 'gate_up'), None if y is None else y.data_ptr(),
+                                        xq.data_ptr(), sx.data_ptr(), m, i2 // 2, stream_ptr()), 'silu_mul_quant')
+    return xq, sx, y
