@@ -145,19 +145,29 @@ int kairos_f16_gemm(const void* X_f16, const void* W16, const void* bias_f16_or_
                     int K, void* workspace, size_t workspace_bytes, kairos_stream_t stream);
 
 /* ---- element-wise operators around the linears of a decoder layer (one pass each) ----------------
+ * These operators, the decode-side kernel, the activation quantization and the single-CTA GEMM are launched
+ * with programmatic stream serialization: each may become resident while the kernel before it in the stream
+ * drains, sets up (and, in the decode-side kernel, starts streaming the packed weights -- which must
+ * therefore not be written by the kernel directly before it) and only then waits for that kernel's
+ * results.  KAIROS_NO_PDL=1 in the environment restores ordinary launches.
  * Counterparts the reference vendors but never calls: rms_norm_general
  * (thirdparty/AWQ/kernels/csrc/w8a8/layernorm.cu:56-231) and silu_and_mul
  * (thirdparty/AWQ/kernels/csrc/w8a8/act.cu:34-140); in its runs these steps are HuggingFace torch code. */
 /* Y[m,:] = half(float(X[m,:]) * rsqrt(mean(X[m,:]^2) + eps) * float(W)); K % 8 == 0, K <= 16384 */
 int kairos_rms_norm(const void* X_f16, const void* W_f16, void* Y_f16, int M, int K, float eps,
                     kairos_stream_t stream);
+/* The residual addition of the layer before, carried by the norm that follows it: X <- half(X + H) in place,
+ * then Y = rms_norm(X).  One pass instead of an element-wise add plus a norm. */
+int kairos_add_rms_norm(void* X_f16_inout, const void* H_f16, const void* W_f16, void* Y_f16, int M, int K, float eps,
+                        kairos_stream_t stream);
 /* Y[m,i] = silu(GU[m,i]) * GU[m,I+i] for the fused gate|up activation GU [M, 2I]; I % 8 == 0 */
 int kairos_silu_mul(const void* GU_f16, void* Y_f16, int M, int I, kairos_stream_t stream);
 /* The same two operators emitting the precision a following W8A8 linear consumes: per-token int8 Xq + fp16
  * scale sx, bit-identical to kairos_act_quant_i8 applied to the fp16 result; the fp16 tensor itself is
- * written only when Y is given.  K % 16 == 0, K <= 16384; I % 16 == 0, I <= 32768. */
-int kairos_rms_norm_quant(const void* X_f16, const void* W_f16, void* Y_f16_or_null, void* Xq_i8, void* sx_f16,
-                          int M, int K, float eps, kairos_stream_t stream);
+ * written only when Y is given.  With H given, X <- X + H first (as in kairos_add_rms_norm).
+ * K % 16 == 0, K <= 16384; I % 16 == 0, I <= 32768. */
+int kairos_rms_norm_quant(void* X_f16, const void* H_f16_or_null, const void* W_f16, void* Y_f16_or_null, void* Xq_i8,
+                          void* sx_f16, int M, int K, float eps, kairos_stream_t stream);
 int kairos_silu_mul_quant(const void* GU_f16, void* Y_f16_or_null, void* Xq_i8, void* sx_f16, int M, int I,
                           kairos_stream_t stream);
 

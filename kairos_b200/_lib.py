@@ -36,7 +36,8 @@ SIGNATURES = {
     'kairos_f16_gemm': (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
     'kairos_rms_norm': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_float, c_void_p]),
     'kairos_silu_mul': (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
-    'kairos_rms_norm_quant': (c_int, [c_void_p] * 5 + [c_int, c_int, ctypes.c_float, c_void_p]),
+    'kairos_rms_norm_quant': (c_int, [c_void_p] * 6 + [c_int, c_int, ctypes.c_float, c_void_p]),
+    'kairos_add_rms_norm': (c_int, [c_void_p] * 4 + [c_int, c_int, ctypes.c_float, c_void_p]),
     'kairos_silu_mul_quant': (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p]),
     'kairos_rope_kv': (c_int, [c_void_p] * 4 + [c_int] + [c_void_p] * 3 + [c_int] * 6 + [c_void_p]),
     'kairos_lut_create': (c_void_p, []),

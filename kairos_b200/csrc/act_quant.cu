@@ -19,6 +19,8 @@ template <int R>   // 16-element chunks per thread, upper bound
 __global__ void __launch_bounds__(kAqThreads) act_quant_kernel(const __half* __restrict__ X,
                                                                int8_t* __restrict__ Xq,
                                                                __half* __restrict__ sx, int K) {
+    chain_release();
+    chain_wait();
     const int token = blockIdx.x;
     const int chunks = K >> 4;
     const uint4* row = reinterpret_cast<const uint4*>(X + (size_t)token * K);
@@ -28,8 +30,8 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_kernel(const __half* __r
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * kAqThreads;
         if (c < chunks) {
-            v[r][0] = __ldg(row + 2 * c);
-            v[r][1] = __ldg(row + 2 * c + 1);
+            v[r][0] = __ldcg(row + 2 * c);
+            v[r][1] = __ldcg(row + 2 * c + 1);
             const __half2* h = reinterpret_cast<const __half2*>(&v[r][0]);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -86,15 +88,17 @@ extern "C" int kairos_act_quant_i8(const void* X, void* Xq, void* sx, int M, int
     int8_t* q = static_cast<int8_t*>(Xq);
     __half* s = static_cast<__half*>(sx);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    cudaError_t e;
     if (per_thread <= 2)
-        act_quant_kernel<2><<<M, kAqThreads, 0, st>>>(x, q, s, K);
+        e = launch_chained(act_quant_kernel<2>, dim3(M), dim3(kAqThreads), 0, st, x, q, s, K);
     else if (per_thread <= 4)
-        act_quant_kernel<4><<<M, kAqThreads, 0, st>>>(x, q, s, K);
+        e = launch_chained(act_quant_kernel<4>, dim3(M), dim3(kAqThreads), 0, st, x, q, s, K);
     else if (per_thread <= 8)
-        act_quant_kernel<8><<<M, kAqThreads, 0, st>>>(x, q, s, K);
+        e = launch_chained(act_quant_kernel<8>, dim3(M), dim3(kAqThreads), 0, st, x, q, s, K);
     else if (per_thread <= 16)
-        act_quant_kernel<16><<<M, kAqThreads, 0, st>>>(x, q, s, K);
+        e = launch_chained(act_quant_kernel<16>, dim3(M), dim3(kAqThreads), 0, st, x, q, s, K);
     else
         return KAIROS_ERR_SHAPE;   // K > 32768
+    if (e != cudaSuccess) return note_cuda_error(e);
     return launch_status();
 }

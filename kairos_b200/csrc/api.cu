@@ -1,6 +1,7 @@
 // Host side of the C ABI: status reporting, the interval LUT, the bounded conversion
 // cache with its workspaces, and the switched-linear dispatch
 // (DynamicLinear._forward, kairos/dynamic_linear.py:131-172).
+#include <cstdlib>
 #include <algorithm>
 #include <cstring>
 #include <mutex>
@@ -17,6 +18,14 @@ int note_cuda_error(cudaError_t e) {
     g_last_error = std::string(cudaGetErrorName(e)) + ": " + cudaGetErrorString(e);
     cudaGetLastError();   // clear the sticky-free error state
     return KAIROS_ERR_CUDA;
+}
+
+bool chained_launch_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("KAIROS_NO_PDL");
+        return !(e && e[0] == '1');
+    }();
+    return on;
 }
 
 int launch_status() {

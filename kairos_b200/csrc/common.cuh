@@ -25,6 +25,36 @@ inline int padded_groups(int K) { return ((K / kGroup + 7) / 8) * 8; }
 int note_cuda_error(cudaError_t e);   // records the message, returns KAIROS_ERR_CUDA
 int launch_status();                  // cudaGetLastError() -> status
 void set_last_error(const char* msg); // detail text returned by kairos_last_error()
+bool chained_launch_enabled();        // false when the environment sets KAIROS_NO_PDL=1
+
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched through launch_chained may become resident while the
+// kernel before it in the stream is still running; it must execute chain_wait() before it touches
+// anything an earlier kernel wrote (or writes anything an earlier kernel reads).  What it does before
+// that -- barrier set-up, descriptor prefetch, streaming of CONSTANT inputs such as the packed weights --
+// overlaps the tail of its predecessor.  chain_release() lets the kernel after it start the same way.
+// Both instructions are no-ops in a kernel launched the ordinary way.
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = chained_launch_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 // ---------------------------------------------------------------------------
 // uint4 unpack.  A 32-bit word of the base holds, for fixed (row, a, c), the

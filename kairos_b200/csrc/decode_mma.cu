@@ -17,6 +17,8 @@
 //     with the stored per-group fp16 factors, in fp32;
 //   * the K slices of a unit (one per consumer warp) meet in shared memory at its end.
 // No scratch memory, no atomics, one launch.  Every wait is bounded (status word on timeout).
+// Launched with programmatic stream serialization: the weight pipeline fills while the kernel before
+// this one in the stream is still draining.
 //
 // Algorithmic bytes per call: K*N/2 + 4*(K/128)*N + 2*M*K + 2*M*N.
 #include <cuda.h>
@@ -112,6 +114,10 @@ __global__ void __launch_bounds__(DecCfg<NT>::kThreads, 1)
         tma_prefetch_desc(&tmap_z);
     }
     __syncthreads();
+    // The kernel after this one may set up now.  This kernel itself streams the packed weights and
+    // their factors (constant inputs) straight away; only the activation producer waits for the
+    // kernel before it, and every output is ordered after the activations it is computed from.
+    chain_release();
 
     if (warp == Cfg::kConsumers) {
         // ---------------- producer: packed weights + scales ----------------
@@ -134,6 +140,7 @@ __global__ void __launch_bounds__(DecCfg<NT>::kThreads, 1)
     } else if (warp == Cfg::kConsumers + 1) {
         // ---------------- producer: activations + scaled zeros ----------------
         if (lane == 0) {
+            chain_wait();
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -349,7 +356,9 @@ static int launch_decode(const void* X, const void* qweight, const void* scales,
     }
     const int sms = device_sm_count();
     const int grid = p.units < sms ? p.units : sms;
-    decode_mma_kernel<NT><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tw, tx, ts, tz, p);
+    const cudaError_t e = launch_chained(decode_mma_kernel<NT>, dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream,
+                                         tw, tx, ts, tz, p);
+    if (e != cudaSuccess) return note_cuda_error(e);
     return launch_status();
 }
 

@@ -117,7 +117,7 @@ __device__ __forceinline__ void store_output(const GemmParams& p, uint32_t v, in
                                              __half bias_n) {
     __half y;
     if constexpr (kInt8) {
-        const float sc = __fmul_rn(s1f, __half2float(__ldg(p.sx + m)));
+        const float sc = __fmul_rn(s1f, __half2float(__ldcg(p.sx + m)));
         y = __float2half_rn(__fmul_rn((float)(int32_t)v, sc));
         if (p.acc_dbg) p.acc_dbg[(size_t)m * p.N + n] = (int32_t)v;
     } else {
@@ -132,6 +132,8 @@ __device__ __forceinline__ void store_output(const GemmParams& p, uint32_t v, in
 // 512-byte row of a partial tile, and the loads of a thread (one per split) are independent.
 template <bool kInt8>
 __global__ void __launch_bounds__(kTileN) splitk_reduce_kernel(const GemmParams p, int bt) {
+    chain_release();
+    chain_wait();
     const int tile = blockIdx.x / bt, c = blockIdx.x % bt;
     const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
     const int n = n_tile * kTileN + threadIdx.x;
@@ -235,6 +237,10 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up above may overlap the kernel before this one; its results (activations, converted weights,
+    // the shared split-K workspace) are touched only after this point
+    chain_release();
+    chain_wait();
 
     const int total_units = p.n_tiles * p.m_tiles * p.splits;
 
@@ -630,11 +636,15 @@ static int launch_one(const GemmArgs& a, const Plan& pl) {
     const int units = pl.n_tiles * pl.m_tiles * pl.splits;
     const int sms = device_sm_count();
     const int grid = units < sms ? units : sms;
-    umma_gemm_kernel<kInt8, kMode, BT><<<grid, Cfg::kThreads, Cfg::kSmemBytes, a.stream>>>(tw, tx, ts, tz, p);
+    cudaError_t e = launch_chained(umma_gemm_kernel<kInt8, kMode, BT>, dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes,
+                                   a.stream, tw, tx, ts, tz, p);
+    if (e != cudaSuccess) return note_cuda_error(e);
     if (pl.splits > 1) {
         const int rc2 = launch_status();
         if (rc2 != KAIROS_OK) return rc2;
-        splitk_reduce_kernel<kInt8><<<pl.n_tiles * pl.m_tiles * BT, kTileN, 0, a.stream>>>(p, BT);
+        e = launch_chained(splitk_reduce_kernel<kInt8>, dim3(pl.n_tiles * pl.m_tiles * BT), dim3(kTileN), 0, a.stream, p,
+                           (int)BT);
+        if (e != cudaSuccess) return note_cuda_error(e);
     }
     return launch_status();
 }

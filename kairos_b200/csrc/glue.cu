@@ -8,20 +8,38 @@
 
 namespace kairos {
 
+// Row chunk of the residual stream: x, or (with a pending delta H) x + h in fp16, which is also written
+// back to X -- the residual addition of the layer before rides in the norm that follows it.
+__device__ __forceinline__ uint4 load_residual(__half* X, const __half* H, size_t row_off, int c) {
+    uint4* xp = reinterpret_cast<uint4*>(X + row_off) + c;
+    uint4 v = __ldcg(xp);
+    if (H) {
+        const uint4 h4 = __ldcg(reinterpret_cast<const uint4*>(H + row_off) + c);
+        __half2* a = reinterpret_cast<__half2*>(&v);
+        const __half2* b = reinterpret_cast<const __half2*>(&h4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = __hadd2(a[i], b[i]);
+        *xp = v;
+    }
+    return v;
+}
+
 // y = half( float(x) * rsqrt(mean(x^2) + eps) * float(w) ), one CTA per token, row kept in registers
 template <int R>
-__global__ void __launch_bounds__(256) rms_norm_kernel(const __half* __restrict__ X, const __half* __restrict__ W,
-                                                       __half* __restrict__ Y, int K, float eps) {
+__global__ void __launch_bounds__(256) rms_norm_kernel(__half* X, const __half* __restrict__ H,
+                                                       const __half* __restrict__ W, __half* __restrict__ Y, int K,
+                                                       float eps) {
+    chain_release();
+    chain_wait();
     const int token = blockIdx.x;
     const int chunks = K >> 3;
-    const uint4* row = reinterpret_cast<const uint4*>(X + (size_t)token * K);
     uint4 v[R];
     float ss = 0.f;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * 256;
         if (c < chunks) {
-            v[r] = __ldg(row + c);
+            v[r] = load_residual(X, H, (size_t)token * K, c);
             const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -63,12 +81,14 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const __half* __restrict_
 // Y[m, i] = half( half(silu(gate)) * up ), gate = GU[m, i], up = GU[m, I + i]
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* __restrict__ GU, __half* __restrict__ Y, int M,
                                                        int I) {
+    chain_release();
+    chain_wait();
     const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;       // one 8-element chunk
     const int per_row = I >> 3;
     if (idx >= (long long)M * per_row) return;
     const int m = (int)(idx / per_row), c = (int)(idx % per_row);
-    const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(GU + (size_t)m * 2 * I) + c);
-    const uint4 u4 = __ldg(reinterpret_cast<const uint4*>(GU + (size_t)m * 2 * I + I) + c);
+    const uint4 g4 = __ldcg(reinterpret_cast<const uint4*>(GU + (size_t)m * 2 * I) + c);
+    const uint4 u4 = __ldcg(reinterpret_cast<const uint4*>(GU + (size_t)m * 2 * I + I) + c);
     const __half2* g = reinterpret_cast<const __half2*>(&g4);
     const __half2* u = reinterpret_cast<const __half2*>(&u4);
     uint4 o4;
@@ -126,20 +146,22 @@ __device__ __forceinline__ float absmax8(const uint4& v) {
 // formed in registers, quantized per token to int8 (+ fp16 scale) and written ONCE as int8; the fp16 tensor
 // is written only when a consumer needs it (Y != null).  Output equals act_quant(rms_norm(X)) bit for bit.
 template <int R>
-__global__ void __launch_bounds__(256) rms_norm_quant_kernel(const __half* __restrict__ X, const __half* __restrict__ W,
-                                                             __half* __restrict__ Y, int8_t* __restrict__ Xq,
-                                                             __half* __restrict__ sx, int K, float eps) {
+__global__ void __launch_bounds__(256) rms_norm_quant_kernel(__half* X, const __half* __restrict__ H,
+                                                             const __half* __restrict__ W, __half* __restrict__ Y,
+                                                             int8_t* __restrict__ Xq, __half* __restrict__ sx, int K,
+                                                             float eps) {
     __shared__ float part[8];
+    chain_release();
+    chain_wait();
     const int token = blockIdx.x;
     const int chunks = K >> 3;
-    const uint4* row = reinterpret_cast<const uint4*>(X + (size_t)token * K);
     uint4 v[R];
     float ss = 0.f;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * 256;
         if (c < chunks) {
-            v[r] = __ldg(row + c);
+            v[r] = load_residual(X, H, (size_t)token * K, c);
             const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -193,6 +215,8 @@ template <int R>
 __global__ void __launch_bounds__(256) silu_mul_quant_kernel(const __half* __restrict__ GU, __half* __restrict__ Y,
                                                              int8_t* __restrict__ Xq, __half* __restrict__ sx, int I) {
     __shared__ float part[8];
+    chain_release();
+    chain_wait();
     const int token = blockIdx.x;
     const int chunks = I >> 3;
     const uint4* gp = reinterpret_cast<const uint4*>(GU + (size_t)token * 2 * I);
@@ -203,7 +227,7 @@ __global__ void __launch_bounds__(256) silu_mul_quant_kernel(const __half* __res
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * 256;
         if (c < chunks) {
-            const uint4 g4 = __ldg(gp + c), u4 = __ldg(up + c);
+            const uint4 g4 = __ldcg(gp + c), u4 = __ldcg(up + c);
             const __half2* g = reinterpret_cast<const __half2*>(&g4);
             const __half2* u = reinterpret_cast<const __half2*>(&u4);
             uint4 o4;
@@ -240,6 +264,8 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const __half* __restrict__
                                                       int pos0_host, __half* __restrict__ Q_out,
                                                       __half* __restrict__ Kc, __half* __restrict__ Vc, int B, int S,
                                                       int H, int Hkv, int D, int max_len) {
+    chain_release();
+    chain_wait();
     const int half_d = D >> 1;
     const int heads = H + 2 * Hkv;
     const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
@@ -250,9 +276,10 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const __half* __restrict__
     const int head = (int)(r % heads);
     r /= heads;
     const int s = (int)(r % S), b = (int)(r / S);
-    const int pos = (pos_dev ? (int)*pos_dev : pos0_host) + s;
+    const int pos = (pos_dev ? (int)__ldcg(pos_dev) : pos0_host) + s;
     const __half* src = QKV + ((size_t)(b * S + s) * heads + head) * D;
-    const float x1 = __half2float(src[d]), x2 = __half2float(src[d + half_d]);
+    const __half h1 = __ldcg(src + d), h2 = __ldcg(src + d + half_d);
+    const float x1 = __half2float(h1), x2 = __half2float(h2);
     if (head < H + Hkv) {
         const float c = __half2float(cosT[(size_t)pos * half_d + d]), sn = __half2float(sinT[(size_t)pos * half_d + d]);
         const __half y1 = __float2half_rn(x1 * c - x2 * sn), y2 = __float2half_rn(x2 * c + x1 * sn);
@@ -262,11 +289,46 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const __half* __restrict__
         dst[d + half_d] = y2;
     } else {
         __half* dst = Vc + (((size_t)b * Hkv + (head - H - Hkv)) * max_len + pos) * D;
-        dst[d] = src[d];
-        dst[d + half_d] = src[d + half_d];
+        dst[d] = h1;
+        dst[d + half_d] = h2;
     }
 }
 
+}  // namespace kairos
+
+namespace kairos {
+static int run_rms_norm(void* X, const void* H, const void* W, void* Y, int M, int K, float eps, cudaStream_t st) {
+    __half* x = static_cast<__half*>(X);
+    const __half* h = static_cast<const __half*>(H);
+    const __half* w = static_cast<const __half*>(W);
+    __half* y = static_cast<__half*>(Y);
+    const int per = (K / 8 + 255) / 256;
+    cudaError_t e;
+    if (per <= 1) e = launch_chained(rms_norm_kernel<1>, dim3(M), dim3(256), 0, st, x, h, w, y, K, eps);
+    else if (per <= 2) e = launch_chained(rms_norm_kernel<2>, dim3(M), dim3(256), 0, st, x, h, w, y, K, eps);
+    else if (per <= 4) e = launch_chained(rms_norm_kernel<4>, dim3(M), dim3(256), 0, st, x, h, w, y, K, eps);
+    else e = launch_chained(rms_norm_kernel<8>, dim3(M), dim3(256), 0, st, x, h, w, y, K, eps);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    return launch_status();
+}
+
+static int run_rms_norm_quant(void* X, const void* H, const void* W, void* Y, void* Xq, void* sx, int M, int K,
+                              float eps, cudaStream_t st) {
+    __half* x = static_cast<__half*>(X);
+    const __half* h = static_cast<const __half*>(H);
+    const __half* w = static_cast<const __half*>(W);
+    __half* y = static_cast<__half*>(Y);
+    int8_t* q = static_cast<int8_t*>(Xq);
+    __half* s = static_cast<__half*>(sx);
+    const int per = (K / 8 + 255) / 256;
+    cudaError_t e;
+    if (per <= 1) e = launch_chained(rms_norm_quant_kernel<1>, dim3(M), dim3(256), 0, st, x, h, w, y, q, s, K, eps);
+    else if (per <= 2) e = launch_chained(rms_norm_quant_kernel<2>, dim3(M), dim3(256), 0, st, x, h, w, y, q, s, K, eps);
+    else if (per <= 4) e = launch_chained(rms_norm_quant_kernel<4>, dim3(M), dim3(256), 0, st, x, h, w, y, q, s, K, eps);
+    else e = launch_chained(rms_norm_quant_kernel<8>, dim3(M), dim3(256), 0, st, x, h, w, y, q, s, K, eps);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    return launch_status();
+}
 }  // namespace kairos
 
 extern "C" int kairos_rms_norm(const void* X, const void* W, void* Y, int M, int K, float eps, kairos_stream_t stream) {
@@ -274,16 +336,18 @@ extern "C" int kairos_rms_norm(const void* X, const void* W, void* Y, int M, int
     if (M < 0 || K <= 0 || (K % 8) != 0 || K > 8 * 256 * 8) return KAIROS_ERR_SHAPE;
     if (M == 0) return KAIROS_OK;
     if (!X || !W || !Y || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)Y & 15)) return KAIROS_ERR_ALIGN;
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    const __half* x = static_cast<const __half*>(X);
-    const __half* w = static_cast<const __half*>(W);
-    __half* y = static_cast<__half*>(Y);
-    const int per = (K / 8 + 255) / 256;
-    if (per <= 1) rms_norm_kernel<1><<<M, 256, 0, st>>>(x, w, y, K, eps);
-    else if (per <= 2) rms_norm_kernel<2><<<M, 256, 0, st>>>(x, w, y, K, eps);
-    else if (per <= 4) rms_norm_kernel<4><<<M, 256, 0, st>>>(x, w, y, K, eps);
-    else rms_norm_kernel<8><<<M, 256, 0, st>>>(x, w, y, K, eps);
-    return launch_status();
+    return run_rms_norm(const_cast<void*>(X), nullptr, W, Y, M, K, eps, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int kairos_add_rms_norm(void* X, const void* H, const void* W, void* Y, int M, int K, float eps,
+                                   kairos_stream_t stream) {
+    using namespace kairos;
+    if (M < 0 || K <= 0 || (K % 8) != 0 || K > 8 * 256 * 8) return KAIROS_ERR_SHAPE;
+    if (M == 0) return KAIROS_OK;
+    if (!X || !H || !W || !Y || ((uintptr_t)X & 15) || ((uintptr_t)H & 15) || ((uintptr_t)W & 15) ||
+        ((uintptr_t)Y & 15))
+        return KAIROS_ERR_ALIGN;
+    return run_rms_norm(X, H, W, Y, M, K, eps, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int kairos_silu_mul(const void* GU, void* Y, int M, int I, kairos_stream_t stream) {
@@ -292,8 +356,10 @@ extern "C" int kairos_silu_mul(const void* GU, void* Y, int M, int I, kairos_str
     if (M == 0) return KAIROS_OK;
     if (!GU || !Y || ((uintptr_t)GU & 15) || ((uintptr_t)Y & 15)) return KAIROS_ERR_ALIGN;
     const long long chunks = (long long)M * (I / 8);
-    silu_mul_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(GU), static_cast<__half*>(Y), M, I);
+    const cudaError_t e = launch_chained(silu_mul_kernel, dim3((unsigned)((chunks + 255) / 256)), dim3(256), 0,
+                                         reinterpret_cast<cudaStream_t>(stream), static_cast<const __half*>(GU),
+                                         static_cast<__half*>(Y), M, I);
+    if (e != cudaSuccess) return note_cuda_error(e);
     return launch_status();
 }
 
@@ -305,33 +371,24 @@ extern "C" int kairos_rope_kv(const void* QKV, const void* cos_table, const void
     if (!pos_dev_or_null && (pos0 < 0 || pos0 + S > max_len)) return KAIROS_ERR_SHAPE;
     if (!QKV || !cos_table || !sin_table || !Q_out || !K_cache || !V_cache) return KAIROS_ERR_ALIGN;
     const long long total = (long long)B * S * (H + 2 * Hkv) * (D / 2);
-    rope_kv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+    const cudaError_t e = launch_chained(
+        rope_kv_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
         static_cast<const __half*>(QKV), static_cast<const __half*>(cos_table), static_cast<const __half*>(sin_table),
         static_cast<const long long*>(pos_dev_or_null), pos0, static_cast<__half*>(Q_out),
         static_cast<__half*>(K_cache), static_cast<__half*>(V_cache), B, S, H, Hkv, D, max_len);
+    if (e != cudaSuccess) return note_cuda_error(e);
     return launch_status();
 }
 
-extern "C" int kairos_rms_norm_quant(const void* X, const void* W, void* Y_or_null, void* Xq, void* sx, int M, int K,
-                                     float eps, kairos_stream_t stream) {
+extern "C" int kairos_rms_norm_quant(void* X, const void* H_or_null, const void* W, void* Y_or_null, void* Xq, void* sx,
+                                     int M, int K, float eps, kairos_stream_t stream) {
     using namespace kairos;
     if (M < 0 || K <= 0 || (K % 16) != 0 || K > 8 * 256 * 8) return KAIROS_ERR_SHAPE;
     if (M == 0) return KAIROS_OK;
     if (!X || !W || !Xq || !sx || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)Xq & 15) ||
-        ((uintptr_t)Y_or_null & 15))
+        ((uintptr_t)Y_or_null & 15) || ((uintptr_t)H_or_null & 15))
         return KAIROS_ERR_ALIGN;
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    const __half* x = static_cast<const __half*>(X);
-    const __half* w = static_cast<const __half*>(W);
-    __half* y = static_cast<__half*>(Y_or_null);
-    int8_t* q = static_cast<int8_t*>(Xq);
-    __half* s = static_cast<__half*>(sx);
-    const int per = (K / 8 + 255) / 256;
-    if (per <= 1) rms_norm_quant_kernel<1><<<M, 256, 0, st>>>(x, w, y, q, s, K, eps);
-    else if (per <= 2) rms_norm_quant_kernel<2><<<M, 256, 0, st>>>(x, w, y, q, s, K, eps);
-    else if (per <= 4) rms_norm_quant_kernel<4><<<M, 256, 0, st>>>(x, w, y, q, s, K, eps);
-    else rms_norm_quant_kernel<8><<<M, 256, 0, st>>>(x, w, y, q, s, K, eps);
-    return launch_status();
+    return run_rms_norm_quant(X, H_or_null, W, Y_or_null, Xq, sx, M, K, eps, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int kairos_silu_mul_quant(const void* GU, void* Y_or_null, void* Xq, void* sx, int M, int I,
@@ -347,8 +404,10 @@ extern "C" int kairos_silu_mul_quant(const void* GU, void* Y_or_null, void* Xq, 
     int8_t* q = static_cast<int8_t*>(Xq);
     __half* s = static_cast<__half*>(sx);
     const int per = (I / 8 + 255) / 256;
-    if (per <= 4) silu_mul_quant_kernel<4><<<M, 256, 0, st>>>(gu, y, q, s, I);
-    else if (per <= 8) silu_mul_quant_kernel<8><<<M, 256, 0, st>>>(gu, y, q, s, I);
-    else silu_mul_quant_kernel<16><<<M, 256, 0, st>>>(gu, y, q, s, I);
+    cudaError_t e;
+    if (per <= 4) e = launch_chained(silu_mul_quant_kernel<4>, dim3(M), dim3(256), 0, st, gu, y, q, s, I);
+    else if (per <= 8) e = launch_chained(silu_mul_quant_kernel<8>, dim3(M), dim3(256), 0, st, gu, y, q, s, I);
+    else e = launch_chained(silu_mul_quant_kernel<16>, dim3(M), dim3(256), 0, st, gu, y, q, s, I);
+    if (e != cudaSuccess) return note_cuda_error(e);
     return launch_status();
 }

@@ -192,29 +192,37 @@ class Decoder(torch.nn.Module):
         self.graph = None
 
     # ---- layers -----------------------------------------------------------------------------
-    def _norm(self, mod, x):
+    def _norm(self, mod, x, delta=None):
+        """RMSNorm of the residual stream; a pending `delta` (output of the block before) is added to x in
+        place by the same pass."""
         if self.glue == 'cuda':
-            return ops.rms_norm(x, mod.weight, mod.eps)
+            return ops.rms_norm(x, mod.weight, mod.eps, residual_delta=delta)
+        if delta is not None:
+            x.add_(delta)
         return mod(x)
 
-    def _qkv(self, a, h):
-        cfg = self.cfg
-        if self.fuse:
-            return a.qkv_proj(h)
-        return torch.cat((a.q_proj(h), a.k_proj(h), a.v_proj(h)), dim=-1)
+    def _norm_then_linear(self, mod, x, delta, lin):
+        """lin(norm(x + delta)); when the LUT sends this M to W8A8 the norm emits the int8 activations that
+        kernel consumes, with no fp16 round trip."""
+        m = x.numel() // x.shape[-1]
+        if self.glue == 'cuda' and self.fuse_quant and lin.wants_int8(m):
+            xq, sx, _ = ops.rms_norm_quant(x, mod.weight, mod.eps, residual_delta=delta)
+            return lin.forward_q8(xq, sx)
+        return lin(self._norm(mod, x, delta))
 
-    def _layer(self, li, layer, x, pos0, decode):
+    def _layer(self, li, layer, x, delta, pos0, decode):
+        """One decoder layer on the residual stream x (updated in place).  `delta` is the output of the
+        previous layer's MLP, not yet added; returns this layer's MLP output in the same way, so that each
+        residual addition is carried by the norm that follows it."""
         cfg = self.cfg
         b, s, _ = x.shape
         nh, nkv, d = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         a = layer.self_attn
-        if self.fuse and self.glue == 'cuda' and self.fuse_quant and a.qkv_proj.wants_int8(b * s):
-            # the norm emits the int8 activations the W8A8 kernel consumes; no fp16 round trip
-            xq, sx, _ = ops.rms_norm_quant(x, layer.input_layernorm.weight, layer.input_layernorm.eps)
-            qkv = a.qkv_proj.forward_q8(xq, sx)
+        if self.fuse:
+            qkv = self._norm_then_linear(layer.input_layernorm, x, delta, a.qkv_proj)   # [B, S, (H + 2 Hkv) D]
         else:
-            h = self._norm(layer.input_layernorm, x)
-            qkv = self._qkv(a, h)                                    # [B, S, (H + 2 Hkv) D]
+            h = self._norm(layer.input_layernorm, x, delta)
+            qkv = torch.cat((a.q_proj(h), a.k_proj(h), a.v_proj(h)), dim=-1)
         kc, vc = self.kv[li, 0], self.kv[li, 1]
         if self.glue == 'cuda':
             q = torch.empty((b, nh, s, d), dtype=torch.float16, device=x.device)
@@ -242,33 +250,31 @@ class Decoder(torch.nn.Module):
             o = F.scaled_dot_product_attention(q, kc[:, :, pos0:pos0 + s], vc[:, :, pos0:pos0 + s], is_causal=True,
                                                enable_gqa=True)
         o = o.transpose(1, 2).reshape(b, s, nh * d)
-        x = x + a.o_proj(o)
+        attn_out = a.o_proj(o)
         m = layer.mlp
-        fq = self.fuse and self.glue == 'cuda' and self.fuse_quant
-        if fq and m.gate_up_proj.wants_int8(b * s):
-            xq, sx, _ = ops.rms_norm_quant(x, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
-            gu = m.gate_up_proj.forward_q8(xq, sx)
-        else:
-            h = self._norm(layer.post_attention_layernorm, x)
-            gu = m.gate_up_proj(h) if self.fuse else None
-        if self.fuse:
-            if fq and m.down_proj.wants_int8(b * s):
-                aq, sa, _ = ops.silu_mul_quant(gu)
-                return x + m.down_proj.forward_q8(aq, sa)
-            act = ops.silu_mul(gu) if self.glue == 'cuda' else F.silu(gu[..., :cfg.inter]) * gu[..., cfg.inter:]
-        else:
-            act = F.silu(m.gate_proj(h)) * m.up_proj(h)
-        x = x + m.down_proj(act)
-        return x
+        if not self.fuse:
+            h = self._norm(layer.post_attention_layernorm, x, attn_out)
+            return m.down_proj(F.silu(m.gate_proj(h)) * m.up_proj(h))
+        gu = self._norm_then_linear(layer.post_attention_layernorm, x, attn_out, m.gate_up_proj)
+        if self.glue == 'cuda' and self.fuse_quant and m.down_proj.wants_int8(b * s):
+            aq, sa, _ = ops.silu_mul_quant(gu)
+            return m.down_proj.forward_q8(aq, sa)
+        act = ops.silu_mul(gu) if self.glue == 'cuda' else F.silu(gu[..., :cfg.inter]) * gu[..., cfg.inter:]
+        return m.down_proj(act)
+
+    def _stack(self, x, decode):
+        """All layers, then the final norm (which carries the last residual addition)."""
+        delta = None
+        for li, layer in enumerate(self.model.layers):
+            delta = self._layer(li, layer, x, delta, 0, decode)
+        return x, delta
 
     @torch.no_grad()
     def prefill(self, tokens, return_logits=False):
         """tokens [B, S] -> next token ids [B, 1]; fills the KV cache for positions 0..S-1."""
         b, s = tokens.shape
-        x = self.embed[tokens]
-        for li, layer in enumerate(self.model.layers):
-            x = self._layer(li, layer, x, 0, False)
-        last = self._norm(self.norm, x[:, -1:, :].contiguous())
+        x, delta = self._stack(self.embed[tokens], False)
+        last = self._norm(self.norm, x[:, -1:, :].contiguous(), None if delta is None else delta[:, -1:, :].contiguous())
         logits = last.reshape(b, -1) @ self.lm_head.t()
         self.mask.fill_(float('-inf'))
         self.mask[..., :s] = 0
@@ -278,11 +284,9 @@ class Decoder(torch.nn.Module):
         return logits.argmax(dim=-1, keepdim=True)
 
     def _decode_body(self):
-        x = self.embed[self.tok]
         self.mask.index_fill_(3, self.pos, 0.0)
-        for li, layer in enumerate(self.model.layers):
-            x = self._layer(li, layer, x, 0, True)
-        self.logits = self._norm(self.norm, x).reshape(x.shape[0], -1) @ self.lm_head.t()
+        x, delta = self._stack(self.embed[self.tok], True)
+        self.logits = self._norm(self.norm, x, delta).reshape(x.shape[0], -1) @ self.lm_head.t()
         self.next_tok.copy_(self.logits.argmax(dim=-1, keepdim=True))
         self.pos.add_(1)
 

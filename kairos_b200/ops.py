@@ -154,15 +154,21 @@ def w8a16_gemm(x, w8, wscales, bias=None):
 
 
 # ---- element-wise operators around the linears ------------------------------------------------
-def rms_norm(x, weight, eps):
-    """RMSNorm over the last dimension of a contiguous fp16 tensor (fp32 arithmetic, one pass)."""
+def rms_norm(x, weight, eps, residual_delta=None):
+    """RMSNorm over the last dimension.  With `residual_delta`, x <- x + residual_delta IN PLACE first (the
+    residual addition of the preceding block, carried by this pass)."""
     k = x.shape[-1]
     m = x.numel() // k
-    out = torch.empty_like(x)
+    y = torch.empty_like(x)
     with torch.cuda.device(x.device):
-        check(lib.kairos_rms_norm(_chk(x, torch.float16, 'x'), _chk(weight, torch.float16, 'weight'), out.data_ptr(),
-                                  m, k, float(eps), stream_ptr()), 'rms_norm')
-    return out
+        if residual_delta is None:
+            check(lib.kairos_rms_norm(_chk(x, torch.float16, 'x'), _chk(weight, torch.float16, 'weight'), y.data_ptr(),
+                                      m, k, float(eps), stream_ptr()), 'rms_norm')
+        else:
+            check(lib.kairos_add_rms_norm(_chk(x, torch.float16, 'x'), _chk(residual_delta, torch.float16, 'delta'),
+                                          _chk(weight, torch.float16, 'weight'), y.data_ptr(), m, k, float(eps),
+                                          stream_ptr()), 'add_rms_norm')
+    return y
 
 
 def silu_mul(gate_up):
@@ -187,17 +193,19 @@ def rope_kv(qkv, cos, sin, q_out, k_cache, v_cache, b, s, h, hkv, d, pos_dev=Non
     return q_out
 
 
-def rms_norm_quant(x, weight, eps, want_f16=False):
+def rms_norm_quant(x, weight, eps, want_f16=False, residual_delta=None):
     """RMSNorm emitting per-token int8 + fp16 scales (what a W8A8 linear consumes); also the fp16 result
-    when `want_f16`.  Returns (xq, sx, y_or_None)."""
+    when `want_f16`; with `residual_delta`, x <- x + residual_delta in place first.
+    Returns (xq, sx, y_or_None)."""
     k = x.shape[-1]
     m = x.numel() // k
     xq = torch.empty(x.shape, dtype=torch.int8, device=x.device)
     sx = torch.empty((m,), dtype=torch.float16, device=x.device)
     y = torch.empty_like(x) if want_f16 else None
     with torch.cuda.device(x.device):
-        check(lib.kairos_rms_norm_quant(_chk(x, torch.float16, 'x'), _chk(weight, torch.float16, 'weight'),
-                                        None if y is None else y.data_ptr(), xq.data_ptr(), sx.data_ptr(), m, k,
+        check(lib.kairos_rms_norm_quant(_chk(x, torch.float16, 'x'),
+                                        None if residual_delta is None else _chk(residual_delta, torch.float16, 'delta'),
+                                        _chk(weight, torch.float16, 'weight'), None if y is None else y.data_ptr(), xq.data_ptr(), sx.data_ptr(), m, k,
                                         float(eps), stream_ptr()), 'rms_norm_quant')
     return xq, sx, y
 

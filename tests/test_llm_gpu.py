@@ -151,3 +151,79 @@ def test_decoder_fused_quant_is_bit_identical():
     finally:
         kb.DynamicLinear.context = None
         kb.DynamicLinear.prof = None
+
+
+def test_add_rms_norm_carries_the_residual_addition():
+    """x <- x + h in place (fp16 addition, as torch does it), then the norm; also in the int8-emitting form."""
+    from kairos_b200 import ops
+    g = torch.Generator('cuda').manual_seed(5)
+    x = (torch.randn(9, 4096, device='cuda', generator=g) * 2).half()
+    h = torch.randn(9, 4096, device='cuda', generator=g).half()
+    w = (1 + 0.1 * torch.randn(4096, device='cuda', generator=g)).half()
+    summed = x + h
+    ref = ops.rms_norm(summed, w, 1e-5)
+    x1 = x.clone()
+    got = ops.rms_norm(x1, w, 1e-5, residual_delta=h)
+    assert torch.equal(x1, summed) and torch.equal(got, ref)
+    x2 = x.clone()
+    xq, sx, y = ops.rms_norm_quant(x2, w, 1e-5, want_f16=True, residual_delta=h)
+    q_ref, s_ref = _act_quant(ref)
+    assert torch.equal(x2, summed) and torch.equal(y, ref)
+    assert torch.equal(xq, q_ref) and torch.equal(sx, s_ref)
+
+
+def test_chained_launches_give_the_same_bits_as_ordinary_launches():
+    """A decode-like chain (norm -> small-batch W4A16 -> SiLU*up -> W4A16, repeated) under programmatic
+    stream serialization, replayed from a CUDA graph, equals the same chain run with a device
+    synchronization after every operator (where no kernel can overlap its predecessor)."""
+    import kairos_b200 as kb
+    from kairos_b200 import ops, runtime, synthetic
+    ctx = runtime.Context('cuda', cache_bytes=None)
+    kb.DynamicLinear.context = ctx
+    try:
+        lins = []
+        for i, (k, n) in enumerate(((1024, 2048), (1024, 1024))):
+            _, w = synthetic.make_case(1, k, n, seed=20 + i)
+            ref_lin = torch.nn.Linear(k, n, bias=False, dtype=torch.float16)
+            ref_lin.weight.data = torch.from_numpy(w.copy()) * 3
+            lins.append(kb.DynamicLinear.from_module(ref_lin.cuda(), 'cuda'))
+        prof = kb.Profiler([l.shape for l in lins])
+        prof.load_table({l.shape: [(30720, 'w4a16_gemv')] for l in lins})
+        kb.DynamicLinear.prof = prof
+        w = torch.ones(1024, device='cuda', dtype=torch.float16)
+        x0 = torch.randn(4, 1, 1024, device='cuda', generator=torch.Generator('cuda').manual_seed(2)).half()
+
+        def chain(x, sync):
+            delta = None
+            for _ in range(6):
+                h = ops.rms_norm(x, w, 1e-5, residual_delta=delta)
+                if sync: torch.cuda.synchronize()
+                gu = lins[0](h)
+                if sync: torch.cuda.synchronize()
+                act = ops.silu_mul(gu)
+                if sync: torch.cuda.synchronize()
+                delta = lins[1](act)
+                if sync: torch.cuda.synchronize()
+            return ops.rms_norm(x, w, 1e-5, residual_delta=delta)
+
+        ref = chain(x0.clone(), True)
+        eager = chain(x0.clone(), False)
+        assert torch.equal(ref, eager)
+        xs = x0.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            chain(xs.clone(), False)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            xin = xs.clone()
+            out = chain(xin, False)
+        for _ in range(3):
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out, ref)
+        assert runtime.device_status() == 0
+    finally:
+        kb.DynamicLinear.context = None
+        kb.DynamicLinear.prof = None
