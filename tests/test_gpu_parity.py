@@ -141,6 +141,36 @@ def test_decode_mma(kb, m, k, n):
     assert_close(y.cpu().numpy(), ko.y_w4a16(x, res), f'decode m={m} k={k} n={n}')
 
 
+@pytest.mark.parametrize('m,k,n', [(2, 4096, 6144), (1, 14336, 256), (12, 2048, 40)])
+def test_decode_mma_launches_in_a_row_and_graph_replays(kb, m, k, n):
+    """Launches in a row (each may start while its predecessor drains) and replays of a captured pair of
+    launches all give the oracle's result."""
+    import torch
+    _, ops, _ = kb
+    x, _, res = case(m, k, n, seed=7 * m)
+    r = resident(res)
+    want = ko.y_w4a16(x, res)
+    xd = dev(x)
+    for i in range(4):
+        y = ops.decode_forward(xd, r['qweight'], r['scales'], r['scaled_zeros'], m, n, k)
+        assert_close(y.cpu().numpy(), want, f'decode launch {i} m={m} k={k} n={n}')
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ops.decode_forward(xd, r['qweight'], r['scales'], r['scaled_zeros'], m, n, k)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        y1 = ops.decode_forward(xd, r['qweight'], r['scales'], r['scaled_zeros'], m, n, k)
+        y2 = ops.decode_forward(xd, r['qweight'], r['scales'], r['scaled_zeros'], m, n, k)
+    for i in range(3):
+        y1.zero_(); y2.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert_close(y1.cpu().numpy(), want, f'replay {i} first m={m} k={k} n={n}')
+        assert torch.equal(y1, y2)
+
+
 def test_decode_mma_bias_vs_reference_fixture(kb):
     _, ops, _ = kb
     g = dict(np.load(os.path.join(GOLDEN, 'small_n96_k1152_m33_bias.npz')))
