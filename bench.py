@@ -465,9 +465,9 @@ def run_gpu_arm(args):
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
 # under profiles/ (same kernels, same shapes as the roofline points below); bytes.
 NCU_TRAFFIC = {
-    'umma_gemm_kernel<int8, tma, BT=256>': 94454784 + 202956288,     # profiles/umma_gemm_int8_M8192_K4096_N14336.md
-    'umma_gemm_kernel<f16, tma, BT=256>': 1334805000 + 228701184,    # profiles/umma_gemm_f16_M8192_K4096_N14336.md
-    'decode': 31218432,                                              # profiles/decode_mma_M1_K4096_N14336.md
+    'umma_gemm_pair_kernel<int8> (cta_group::2, 256x256)': 114348544 + 202551040,   # profiles/umma_gemm_pair_int8_M8192_K4096_N14336.md
+    'umma_gemm_pair_kernel<f16> (cta_group::2, 256x256)': 958190080 + 222985216,    # profiles/umma_gemm_pair_f16_M8192_K4096_N14336.md
+    'decode': 31219200,                                                              # profiles/decode_mma_M1_K4096_N14336.md
 }
 
 
@@ -505,12 +505,12 @@ def dominant_rooflines(torch, kb, mods, xs_dev, prof, peaks, flush, l2_bytes):
         y = torch.empty((m, n), dtype=torch.float16, device=x.device)
         t = time_call(lambda: ops.w8a8_gemm_forward_cuda(xq, w8, mod.scales_1, sx, y))
         peak, peak_note = 2 * peaks['bf16_tflops'], '2 x measured bf16 burst (int8 is nominally 2x bf16)'
-        kern = 'umma_gemm_kernel<int8, tma, BT=256>'
+        kern = 'umma_gemm_pair_kernel<int8> (cta_group::2, 256x256)'
     elif cid == 5:
         w16 = mod._trans_weight_to_16()
         t = time_call(lambda: ops.f16_gemm(x, w16))
         peak, peak_note = peaks['bf16_tflops'], 'measured bf16 burst'
-        kern = 'umma_gemm_kernel<f16, tma, BT=256>'
+        kern = 'umma_gemm_pair_kernel<f16> (cta_group::2, 256x256)'
     elif cid == 3:
         w8 = mod._trans_weight_to_8()
         t = time_call(lambda: ops.w8a16_gemm(x, w8, mod.scales_1))
