@@ -17,6 +17,7 @@
 // Every mbarrier wait is bounded (status word on timeout); the two cluster-wide barriers at start and end
 // are reached by every thread on every path.
 #include <cuda.h>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -206,22 +207,23 @@ __global__ void __launch_bounds__(kP2Threads, 1)
             if constexpr (kInt8) s1f = n_ok ? __half2float(__ldg(p.s1 + n)) : 0.f;
             const bool has_bias = p.bias != nullptr;
             const __half bias_n = (has_bias && n_ok) ? __ldg(p.bias + n) : __float2half_rn(0.f);
-            if (!mbar_wait(&tmem_full[b], (it >> 1) & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kP2Tokens);
-#pragma unroll 1
-            for (int c0 = 0; c0 < kP2Tokens; c0 += 16) {
-                uint32_t r[16];
-                tmem_ld16(taddr + c0, r);
-                tmem_ld_wait();
+            // activation scales of 64 token columns, two per lane, fetched one chunk ahead and handed round by
+            // shuffle: a load per column between the stores would stall the only epilogue warp of a scheduler
+            auto load_sx32 = [&](int m_first) {
+                const int m = m_first + lane;
+                return (kInt8 && m < p.M) ? __half2float(__ldg(p.sx + m)) : 0.f;
+            };
+            // 64 accumulator columns of this lane's weight row: scale, round, add bias, store
+            auto emit = [&](const uint32_t (&r)[64], int c0, float sx0, float sx1) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
+                for (int c = 0; c < 64; ++c) {
                     const int m = m_tile * kP2Tokens + c0 + c;
+                    const float sxf = kInt8 ? __shfl_sync(0xffffffffu, c < 32 ? sx0 : sx1, c & 31) : 0.f;
                     if (!n_ok || m >= p.M) continue;
                     __half y;
                     if constexpr (kInt8) {
                         // half(float(acc) * (float(s1[n]) * float(sx[m])))
-                        const float sc = __fmul_rn(s1f, __half2float(__ldg(p.sx + m)));
+                        const float sc = __fmul_rn(s1f, sxf);
                         y = __float2half_rn(__fmul_rn((float)(int32_t)r[c], sc));
                         if (p.acc_dbg) p.acc_dbg[(size_t)m * p.N + n] = (int32_t)r[c];
                     } else {
@@ -230,6 +232,24 @@ __global__ void __launch_bounds__(kP2Threads, 1)
                     if (has_bias) y = __hadd(y, bias_n);
                     p.Y[(size_t)m * p.N + n] = y;
                 }
+            };
+            float sx_a = load_sx32(m_tile * kP2Tokens), sx_b = load_sx32(m_tile * kP2Tokens + 32);
+            if (!mbar_wait(&tmem_full[b], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kP2Tokens);
+            // Few, large TMEM loads: with 16-column loads this kernel took 441 us on M=8192, K=4096, N=14336
+            // (int8), with 64-column loads 374 us; the mainloop alone (no epilogue) runs in 280 us.
+#pragma unroll 1
+            for (int c0 = 0; c0 < kP2Tokens; c0 += 64) {
+                const float s0 = sx_a, s1 = sx_b;
+                if (c0 + 64 < kP2Tokens) {
+                    sx_a = load_sx32(m_tile * kP2Tokens + c0 + 64);
+                    sx_b = load_sx32(m_tile * kP2Tokens + c0 + 96);
+                }
+                uint32_t r[64];
+                tmem_ld64(taddr + c0, r);
+                tmem_ld_wait();
+                emit(r, c0, s0, s1);
             }
             tc_fence_before();
             __syncwarp();

@@ -113,11 +113,11 @@ __device__ __forceinline__ void widen_s8x4(uint32_t w, __half2 s, __half2& lo, _
 //   int8: half(float(acc) * (float(s1[n]) * float(sx[m])))
 //         (thirdparty/AWQ/kernels/csrc/w8a8/w8a8_gemm_cuda.cu:896-901)
 template <bool kInt8>
-__device__ __forceinline__ void store_output(const GemmParams& p, uint32_t v, int m, int n, float s1f, bool has_bias,
-                                             __half bias_n) {
+__device__ __forceinline__ void store_output(const GemmParams& p, uint32_t v, int m, int n, float s1f, float sxf,
+                                             bool has_bias, __half bias_n) {
     __half y;
     if constexpr (kInt8) {
-        const float sc = __fmul_rn(s1f, __half2float(__ldcg(p.sx + m)));
+        const float sc = __fmul_rn(s1f, sxf);
         y = __float2half_rn(__fmul_rn((float)(int32_t)v, sc));
         if (p.acc_dbg) p.acc_dbg[(size_t)m * p.N + n] = (int32_t)v;
     } else {
@@ -161,7 +161,9 @@ __global__ void __launch_bounds__(kTileN) splitk_reduce_kernel(const GemmParams 
     if constexpr (kInt8) s1f = __half2float(__ldg(p.s1 + n));
     const bool has_bias = p.bias != nullptr;
     const __half bias_n = has_bias ? __ldg(p.bias + n) : __float2half_rn(0.f);
-    store_output<kInt8>(p, acc, m, n, s1f, has_bias, bias_n);
+    float sxf = 0.f;
+    if constexpr (kInt8) sxf = __half2float(__ldcg(p.sx + m));
+    store_output<kInt8>(p, acc, m, n, s1f, sxf, has_bias, bias_n);
 }
 
 // The k-block range of a work unit.  Ranges start and end on multiples of the stage bundle; k blocks
@@ -351,24 +353,41 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
             const bool has_bias = p.bias != nullptr;
             const __half bias_n = (has_bias && n_ok) ? __ldg(p.bias + n) : __float2half_rn(0.f);
 
+            // Token columns are read from TMEM in chunks of kChunk (large loads: the number of loads, not their
+            // size, sets the time of the epilogue) and the activation scales of a chunk, one or two per lane,
+            // are fetched one chunk ahead and handed round by shuffle.
+            constexpr int kChunk = BT >= 64 ? 64 : 16;
+            const bool scaled = kInt8 && p.splits == 1;
+            auto load_sx = [&](int m_first) {
+                const int m = m_first + lane;
+                return (scaled && (kChunk > 16 || lane < 16) && m < p.M) ? __half2float(__ldcg(p.sx + m)) : 0.f;
+            };
+            float sx_a = load_sx(u.m_tile * BT), sx_b = kChunk > 32 ? load_sx(u.m_tile * BT + 32) : 0.f;
             if (!mbar_wait(&tmem_full[b], (it >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BT);
             uint32_t* part = p.partials + ((size_t)unit * BT) * kTileN + row;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BT; c0 += 16) {
-                uint32_t r[16];
-                tmem_ld16(taddr + c0, r);
+            for (int c0 = 0; c0 < BT; c0 += kChunk) {
+                const float s0 = sx_a, s1 = sx_b;
+                if (c0 + kChunk < BT) {
+                    sx_a = load_sx(u.m_tile * BT + c0 + kChunk);
+                    if (kChunk > 32) sx_b = load_sx(u.m_tile * BT + c0 + kChunk + 32);
+                }
+                uint32_t r[kChunk];
+                if constexpr (kChunk == 64) tmem_ld64(taddr + c0, r);
+                else tmem_ld16(taddr + c0, r);
                 tmem_ld_wait();
                 if (p.splits == 1) {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
+                    for (int c = 0; c < kChunk; ++c) {
                         const int m = u.m_tile * BT + c0 + c;
-                        if (n_ok && m < p.M) store_output<kInt8>(p, r[c], m, n, s1f, has_bias, bias_n);
+                        const float sxf = kInt8 ? __shfl_sync(0xffffffffu, c < 32 ? s0 : s1, c & 31) : 0.f;
+                        if (n_ok && m < p.M) store_output<kInt8>(p, r[c], m, n, s1f, sxf, has_bias, bias_n);
                     }
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) part[(size_t)(c0 + c) * kTileN] = r[c];
+                    for (int c = 0; c < kChunk; ++c) part[(size_t)(c0 + c) * kTileN] = r[c];
                 }
             }
             tc_fence_before();
