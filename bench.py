@@ -334,23 +334,48 @@ def run_gpu_arm(args):
         return ms / args.steps
 
     # The step as a CUDA graph: one pass of module forwards captured once, replayed per step (launch
-    # latency of the 56 small calls is then off the critical path).  At N > 1 the pass stays eager: the
-    # NCCL all-reduces are not captured.
+    # latency of the 56 small calls is then off the critical path).  At N > 1 the NCCL all-reduces are
+    # not captured: each shape's 14 local linears are one graph, and the all-reduces of a row-parallel
+    # shape are issued (async) right after its graph, so they run while the next shapes compute.
     step_fn, mode = one_pass, 'eager'
-    if world == 1:
-        try:
-            side = torch.cuda.Stream()
-            with torch.cuda.stream(side):
-                for _ in range(2):
-                    one_pass()
-            torch.cuda.synchronize()
+    try:
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                for li, kn in enumerate(SHAPES_KN):
+                    for m in M_LIST:
+                        mods[li](xs_dev[kn][:m].unsqueeze(0))
+        torch.cuda.synchronize()
+        if world == 1:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 one_pass()
             step_fn, mode = graph.replay, 'cuda-graph'
-        except Exception as exc:       # keep measuring, say why the graph was not used
-            mode = f'eager (graph capture failed: {type(exc).__name__})'
-            torch.cuda.synchronize()
+        else:
+            graphs, outs = [], []
+            for li, kn in enumerate(SHAPES_KN):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    ys = [mods[li](xs_dev[kn][:m].unsqueeze(0)) for m in M_LIST]
+                graphs.append(g)
+                outs.append(ys)
+            reduced = [isinstance(l, tp.RowParallelLinear) for l in layers]
+            # row-parallel shapes first: their reductions then overlap the column-parallel shapes' compute
+            order = sorted(range(len(SHAPES_KN)), key=lambda li: not reduced[li])
+
+            def step_tp():
+                works = []
+                for li in order:
+                    graphs[li].replay()
+                    if reduced[li]:
+                        works += [dist.all_reduce(y, op=dist.ReduceOp.SUM, async_op=True) for y in outs[li]]
+                for w in works:
+                    w.wait()                     # orders the compute stream after the reductions
+
+            step_fn, mode = step_tp, 'cuda-graph per shape (row-parallel shapes first) + async all-reduce per row-parallel output'
+    except Exception as exc:       # keep measuring, say why the graph was not used
+        mode = f'eager (graph capture failed: {type(exc).__name__})'
+        torch.cuda.synchronize()
 
     sampler = ClockSampler(local)
     if rank == 0:
