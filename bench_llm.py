@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""TTFT / TPOT of a random-init decoder whose linears are switched linears (BASELINE configs 2-3).
+"""TTFT / TPOT of a random-init decoder whose linears are switched linears (the reference's end-to-end latency benchmark: Llama-3-8B, Qwen2-7B, Llama-3-70B geometries).
 
     python bench_llm.py --model llama3-8b --batches 2,4,8,16,32 --prompt 1024 --new 512
 

@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Kernel-switch frequency under continuous batching (BASELINE config 3: Qwen2-7B geometry).
+"""Kernel-switch frequency under continuous batching (the reference's switch-frequency experiment, Qwen2-7B geometry).
 
 64 requests with prompt lengths drawn lognormal(mu = ln 512, sigma = 1.0), clipped to 16..8192, 256 output
 tokens each, are scheduled by a token-budget continuous batcher (prefill chunks and decode tokens share a
