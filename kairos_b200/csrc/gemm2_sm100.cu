@@ -213,11 +213,30 @@ __global__ void __launch_bounds__(kP2Threads, 1)
                 const int m = m_first + lane;
                 return (kInt8 && m < p.M) ? __half2float(__ldg(p.sx + m)) : 0.f;
             };
-            // 64 accumulator columns of this lane's weight row: scale, round, add bias, store
+            // 64 accumulator columns of this lane's weight row: scale, round, add bias, store.  The common
+            // case (tile inside the matrix, no bias, no accumulator dump) runs without per-element checks.
             auto emit = [&](const uint32_t (&r)[64], int c0, float sx0, float sx1) {
+                const int m0 = m_tile * kP2Tokens + c0;
+                const bool plain = n_ok && m0 + 64 <= p.M && !has_bias && p.acc_dbg == nullptr;
+                if (__all_sync(0xffffffffu, plain)) {
+                    __half* yp = p.Y + (size_t)m0 * p.N + n;
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {
+                        __half y;
+                        if constexpr (kInt8) {
+                            const float sxf = __shfl_sync(0xffffffffu, c < 32 ? sx0 : sx1, c & 31);
+                            y = __float2half_rn(__fmul_rn((float)(int32_t)r[c], __fmul_rn(s1f, sxf)));
+                        } else {
+                            y = __float2half_rn(__uint_as_float(r[c]));
+                        }
+                        *yp = y;
+                        yp += p.N;
+                    }
+                    return;
+                }
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
-                    const int m = m_tile * kP2Tokens + c0 + c;
+                    const int m = m0 + c;
                     const float sxf = kInt8 ? __shfl_sync(0xffffffffu, c < 32 ? sx0 : sx1, c & 31) : 0.f;
                     if (!n_ok || m >= p.M) continue;
                     __half y;
@@ -237,8 +256,10 @@ __global__ void __launch_bounds__(kP2Threads, 1)
             if (!mbar_wait(&tmem_full[b], (it >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kP2Tokens);
-            // Few, large TMEM loads: with 16-column loads this kernel took 441 us on M=8192, K=4096, N=14336
-            // (int8), with 64-column loads 374 us; the mainloop alone (no epilogue) runs in 280 us.
+            // Few, large TMEM loads and a lean store loop: on M=8192, K=4096, N=14336 (int8) this kernel took
+            // 441 us with 16-column loads, 374 us with 64-column loads, 320 us once the common case dropped its
+            // per-element checks; the mainloop alone (no epilogue) runs in 280 us, and so does the kernel with
+            // the TMEM loads but no arithmetic or stores: the epilogue's instructions are what is left.
 #pragma unroll 1
             for (int c0 = 0; c0 < kP2Tokens; c0 += 64) {
                 const float s0 = sx_a, s1 = sx_b;

@@ -379,11 +379,28 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                 else tmem_ld16(taddr + c0, r);
                 tmem_ld_wait();
                 if (p.splits == 1) {
+                    const int m0 = u.m_tile * BT + c0;
+                    const bool plain = n_ok && m0 + kChunk <= p.M && !has_bias && p.acc_dbg == nullptr;
+                    if (__all_sync(0xffffffffu, plain)) {
+                        // the common case (chunk inside the matrix, no bias): no per-element checks
+                        __half* yp = p.Y + (size_t)m0 * p.N + n;
 #pragma unroll
-                    for (int c = 0; c < kChunk; ++c) {
-                        const int m = u.m_tile * BT + c0 + c;
-                        const float sxf = kInt8 ? __shfl_sync(0xffffffffu, c < 32 ? s0 : s1, c & 31) : 0.f;
-                        if (n_ok && m < p.M) store_output<kInt8>(p, r[c], m, n, s1f, sxf, has_bias, bias_n);
+                        for (int c = 0; c < kChunk; ++c) {
+                            if constexpr (kInt8) {
+                                const float sxf = __shfl_sync(0xffffffffu, c < 32 ? s0 : s1, c & 31);
+                                *yp = __float2half_rn(__fmul_rn((float)(int32_t)r[c], __fmul_rn(s1f, sxf)));
+                            } else {
+                                *yp = __float2half_rn(__uint_as_float(r[c]));
+                            }
+                            yp += p.N;
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < kChunk; ++c) {
+                            const int m = m0 + c;
+                            const float sxf = kInt8 ? __shfl_sync(0xffffffffu, c < 32 ? s0 : s1, c & 31) : 0.f;
+                            if (n_ok && m < p.M) store_output<kInt8>(p, r[c], m, n, s1f, sxf, has_bias, bias_n);
+                        }
                     }
                 } else {
 #pragma unroll

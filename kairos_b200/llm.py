@@ -161,6 +161,7 @@ class Decoder(torch.nn.Module):
             self.model.layers.append(layer)
         self.kv = None
         self.graph = None
+        self._prefill_graphs = {}
 
     def linear_shapes(self):
         """Distinct (N, K) of this model's switched linears (the LUT's key set)."""
@@ -190,6 +191,7 @@ class Decoder(torch.nn.Module):
         self.mask = torch.full((1, 1, 1, max_len), float('-inf'), dtype=torch.float16, device=self.device)
         self.next_tok = torch.zeros((batch, 1), dtype=torch.long, device=self.device)
         self.graph = None
+        self._prefill_graphs = {}
 
     # ---- layers -----------------------------------------------------------------------------
     def _norm(self, mod, x, delta=None):
@@ -269,9 +271,7 @@ class Decoder(torch.nn.Module):
             delta = self._layer(li, layer, x, delta, 0, decode)
         return x, delta
 
-    @torch.no_grad()
-    def prefill(self, tokens, return_logits=False):
-        """tokens [B, S] -> next token ids [B, 1]; fills the KV cache for positions 0..S-1."""
+    def _prefill_body(self, tokens):
         b, s = tokens.shape
         x, delta = self._stack(self.embed[tokens], False)
         last = self._norm(self.norm, x[:, -1:, :].contiguous(), None if delta is None else delta[:, -1:, :].contiguous())
@@ -279,6 +279,37 @@ class Decoder(torch.nn.Module):
         self.mask.fill_(float('-inf'))
         self.mask[..., :s] = 0
         self.pos.fill_(s)
+        return logits
+
+    @torch.no_grad()
+    def prefill(self, tokens, return_logits=False, use_graph=False):
+        """tokens [B, S] -> next token ids [B, 1]; fills the KV cache for positions 0..S-1.
+
+        use_graph: replay a CUDA graph captured for this (B, S) (the ~500 launches of a prefill are then off
+        the host's critical path); the prompt is copied into the graph's static token buffer.  The graph is
+        captured after two eager passes, so every converted weight it needs is in the conversion cache."""
+        if not use_graph:
+            logits = self._prefill_body(tokens)
+        else:
+            key = tuple(tokens.shape)
+            entry = self._prefill_graphs.get(key)
+            if entry is None:
+                static_tokens = tokens.clone()
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    for _ in range(2):
+                        self._prefill_body(static_tokens)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    static_logits = self._prefill_body(static_tokens)
+                torch.cuda.synchronize()
+                entry = self._prefill_graphs[key] = (graph, static_tokens, static_logits)
+            graph, static_tokens, static_logits = entry
+            static_tokens.copy_(tokens)
+            graph.replay()
+            logits = static_logits
         if return_logits:
             return logits
         return logits.argmax(dim=-1, keepdim=True)
@@ -316,7 +347,7 @@ class Decoder(torch.nn.Module):
 
     @torch.no_grad()
     def generate(self, tokens, max_new_tokens, use_graph=True):
-        nxt = self.prefill(tokens)
+        nxt = self.prefill(tokens, use_graph=use_graph)
         out = [nxt]
         for _ in range(max_new_tokens - 1):
             self.tok.copy_(nxt)
@@ -340,7 +371,7 @@ def measure_ttft_tpot(model, batch, prompt_len=1024, new_tokens=512, warmup=2, t
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(ttft_times):
-        model.prefill(tokens)
+        model.prefill(tokens, use_graph=True)
         torch.cuda.synchronize()
     ttft = (time.perf_counter() - t0) / ttft_times
     torch.cuda.synchronize()

@@ -227,3 +227,32 @@ def test_chained_launches_give_the_same_bits_as_ordinary_launches():
     finally:
         kb.DynamicLinear.context = None
         kb.DynamicLinear.prof = None
+
+
+def test_prefill_graph_equals_eager_prefill():
+    """Replaying the captured prefill of a (B, S) gives the bits of the eager prefill, also for a second
+    prompt of the same shape."""
+    import kairos_b200 as kb
+    from kairos_b200 import llm, runtime
+    cfg = llm.DecoderConfig('tiny', 2, 512, 8, 2, 64, 1024, 1000, 1e-5, 10000.0, True)
+    ctx = runtime.Context('cuda', cache_bytes=None)
+    kb.DynamicLinear.context = ctx
+    try:
+        model = llm.Decoder(cfg, 'cuda', fuse_linears=True, glue='cuda')
+        prof = kb.Profiler(model.linear_shapes())
+        prof.load_table({s: [(8, 'w4a16_gemv'), (64, 'w4a16_gemm'), (30720, 'w8a8')] for s in model.linear_shapes()})
+        kb.DynamicLinear.prof = prof
+        gen = torch.Generator('cuda').manual_seed(4)
+        model.allocate(2, 96)
+        for _ in range(2):
+            tokens = torch.randint(0, cfg.vocab, (2, 48), device='cuda', generator=gen)
+            eager = model.prefill(tokens, return_logits=True).clone()
+            kv_eager = model.kv.clone()
+            model.kv.zero_()
+            replay = model.prefill(tokens, return_logits=True, use_graph=True).clone()
+            assert torch.equal(eager, replay)
+            assert torch.equal(kv_eager, model.kv)
+            assert int(model.pos.item()) == 48
+    finally:
+        kb.DynamicLinear.context = None
+        kb.DynamicLinear.prof = None
