@@ -1,11 +1,17 @@
 // Large-M GEMMs on CTA pairs: Y[M,N] = X . W^T with both operands staged by TMA (W8A8 kind::i8 and FP16
-// kind::f16), one 256 (weight rows) x 256 (tokens) tile per cluster of two CTAs.
+// kind::f16), one 256 (tokens) x 256 (weight rows) tile per cluster of two CTAs.
 //
 // Why pairs: with one CTA per 128 x 256 tile the int8 MMA drains its shared-memory operands (48 KB per
 // 128-byte k block) faster than one SM's shared memory can deliver them (tensor pipe 50 % active).  With
-// tcgen05.mma.cta_group::2 each CTA stages its own 128 weight rows and only HALF of the token tile
-// (32 KB per k block), the pair's tensor cores share the operands, and each CTA keeps its 128 x 256
-// accumulator in its own TMEM.
+// tcgen05.mma.cta_group::2 each CTA stages 128 tokens (its half of the MMA's M = 256) and only HALF of
+// the weight tile (32 KB per k block), the pair's tensor cores share the operands, and each CTA keeps
+// its 128 x 256 accumulator in its own TMEM.
+//
+// Tokens sit on the MMA's M here (unlike the one-CTA kernel, where few tokens must go on N): a TMEM lane
+// is then a token and the accumulator columns are consecutive n, i.e. consecutive addresses of a row of
+// Y, so the epilogue stores 16 bytes per instruction and needs no address arithmetic per element.  The
+// epilogue's instruction stream is what this kernel loses to its mainloop (it shares schedulers with the
+// TMA- and MMA-issuing threads), so its length matters.
 //
 // Protocol (no multicast anywhere):
 //   * both CTAs issue plain TMA loads into their own shared memory; the loads of both signal the FULL
@@ -28,9 +34,9 @@ int make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* ba
 int device_sm_count();        // gemm_sm100.cu
 int* device_status_word();    // api.cu
 
-constexpr int kP2Rows = 128;                       // weight rows per CTA (256 per pair)
-constexpr int kP2Tokens = 256;                     // tokens per tile (128 staged by each CTA)
-constexpr int kP2StageBytes = 2 * kP2Rows * 128;   // A tile + half of the token tile, one 128-byte k block
+constexpr int kP2Rows = 128;                       // rows of either operand staged per CTA (256 per pair)
+constexpr int kP2Tokens = 256;                     // tokens per tile = weight rows per tile
+constexpr int kP2StageBytes = 2 * kP2Rows * 128;   // 128 tokens + 128 weight rows, one 128-byte k block
 constexpr int kP2Stages = 6;
 constexpr int kP2Threads = 32 * 7;
 constexpr int kP2SmemBytes = kP2Stages * kP2StageBytes + 8 * (2 * kP2Stages + 4) + 64 + 1024;
@@ -109,7 +115,7 @@ __global__ void __launch_bounds__(kP2Threads, 1)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
     const bool leader = rank == 0;
-    // pair-wide instruction: M = 256 (128 rows per CTA), N = 256
+    // pair-wide instruction: M = 256 (128 tokens per CTA), N = 256 weight rows
     constexpr uint32_t kIdesc = (kInt8 ? (2u << 4) | (1u << 7) | (1u << 10) : (1u << 4)) |
                                 ((uint32_t)(kP2Tokens >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 
@@ -154,7 +160,7 @@ __global__ void __launch_bounds__(kP2Threads, 1)
                 const int row0 = is_w ? n_tile * 256 + (int)rank * kP2Rows : m_tile * kP2Tokens + (int)rank * 128;
                 for (int kb = 0; kb < p.kb_total; ++kb) {
                     if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
-                    uint8_t* st = smem + s * kP2StageBytes + (is_w ? 0 : kP2Rows * 128);
+                    uint8_t* st = smem + s * kP2StageBytes + (is_w ? kP2Rows * 128 : 0);   // A = tokens, B = weights
                     if (leader) mbar_arrive_expect_tx(&full[s], 2 * kP2Rows * 128);   // this CTA's bytes + the peer's
                     tma_load_3d_pair(st, is_w ? (const void*)&tmap_w : (const void*)&tmap_x,
                                      peer_addr(smem_u32(&full[s]), 0), 0, row0, kb);
@@ -194,56 +200,69 @@ __global__ void __launch_bounds__(kP2Threads, 1)
         }
     } else {
         // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+        // lane = token, accumulator column = weight row n
         const int q = warp & 3;
         const int row = q * 32 + lane;
+        const bool has_bias = p.bias != nullptr;
+        const bool vec_ok = (p.N % 8) == 0 && ((uintptr_t)p.Y & 15) == 0 && !has_bias && p.acc_dbg == nullptr;
         int it = 0;
         bool ok = true;
         for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++it) {
             const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
-            const int n = n_tile * 256 + (int)rank * kP2Rows + row;
-            const bool n_ok = n < p.N;
+            const int m = m_tile * kP2Tokens + (int)rank * kP2Rows + row;
+            const bool m_ok = m < p.M;
+            const int n_base = n_tile * 256;
             const int b = it & 1;
-            float s1f = 0.f;
-            if constexpr (kInt8) s1f = n_ok ? __half2float(__ldg(p.s1 + n)) : 0.f;
-            const bool has_bias = p.bias != nullptr;
-            const __half bias_n = (has_bias && n_ok) ? __ldg(p.bias + n) : __float2half_rn(0.f);
-            // activation scales of 64 token columns, two per lane, fetched one chunk ahead and handed round by
-            // shuffle: a load per column between the stores would stall the only epilogue warp of a scheduler
-            auto load_sx32 = [&](int m_first) {
-                const int m = m_first + lane;
-                return (kInt8 && m < p.M) ? __half2float(__ldg(p.sx + m)) : 0.f;
+            float sxf = 0.f;
+            if constexpr (kInt8) sxf = m_ok ? __half2float(__ldg(p.sx + m)) : 0.f;
+            // per-column factors of 64 columns, two per lane, handed round by shuffle
+            auto load_s1 = [&](int n_first) {
+                const int n = n_first + lane;
+                return (kInt8 && n < p.N) ? __half2float(__ldg(p.s1 + n)) : 0.f;
             };
-            // 64 accumulator columns of this lane's weight row: scale, round, add bias, store.  The common
-            // case (tile inside the matrix, no bias, no accumulator dump) runs without per-element checks.
-            auto emit = [&](const uint32_t (&r)[64], int c0, float sx0, float sx1) {
-                const int m0 = m_tile * kP2Tokens + c0;
-                const bool plain = n_ok && m0 + 64 <= p.M && !has_bias && p.acc_dbg == nullptr;
-                if (__all_sync(0xffffffffu, plain)) {
-                    __half* yp = p.Y + (size_t)m0 * p.N + n;
+            auto load_bias = [&](int n_first) {
+                const int n = n_first + lane;
+                return (has_bias && n < p.N) ? __ldg(p.bias + n) : __float2half_rn(0.f);
+            };
+            // 64 accumulator columns of this lane's token: scale, round, (add bias,) store
+            auto emit = [&](const uint32_t (&r)[64], int c0, float s1a, float s1b) {
+                const int n0 = n_base + c0;
+                if (vec_ok && n0 + 64 <= p.N) {
+                    // the common case: 16-byte stores of 8 consecutive n, no per-element checks
+                    uint4* yp = reinterpret_cast<uint4*>(p.Y + (size_t)m * p.N + n0);
 #pragma unroll
-                    for (int c = 0; c < 64; ++c) {
-                        __half y;
-                        if constexpr (kInt8) {
-                            const float sxf = __shfl_sync(0xffffffffu, c < 32 ? sx0 : sx1, c & 31);
-                            y = __float2half_rn(__fmul_rn((float)(int32_t)r[c], __fmul_rn(s1f, sxf)));
-                        } else {
-                            y = __float2half_rn(__uint_as_float(r[c]));
+                    for (int j = 0; j < 8; ++j) {
+                        __half2 h[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 8 * j + 2 * e;
+                            float v0, v1;
+                            if constexpr (kInt8) {
+                                // half(float(acc) * (float(s1[n]) * float(sx[m])))
+                                const float f0 = __shfl_sync(0xffffffffu, c < 32 ? s1a : s1b, c & 31);
+                                const float f1 = __shfl_sync(0xffffffffu, c + 1 < 32 ? s1a : s1b, (c + 1) & 31);
+                                v0 = __fmul_rn((float)(int32_t)r[c], __fmul_rn(f0, sxf));
+                                v1 = __fmul_rn((float)(int32_t)r[c + 1], __fmul_rn(f1, sxf));
+                            } else {
+                                v0 = __uint_as_float(r[c]);
+                                v1 = __uint_as_float(r[c + 1]);
+                            }
+                            h[e] = __floats2half2_rn(v0, v1);
                         }
-                        *yp = y;
-                        yp += p.N;
+                        if (m_ok) yp[j] = *reinterpret_cast<const uint4*>(h);
                     }
                     return;
                 }
+                const __half ba = load_bias(n0), bb = load_bias(n0 + 32);
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
-                    const int m = m0 + c;
-                    const float sxf = kInt8 ? __shfl_sync(0xffffffffu, c < 32 ? sx0 : sx1, c & 31) : 0.f;
-                    if (!n_ok || m >= p.M) continue;
+                    const int n = n0 + c;
+                    const float s1f = kInt8 ? __shfl_sync(0xffffffffu, c < 32 ? s1a : s1b, c & 31) : 0.f;
+                    const __half bias_n = __shfl_sync(0xffffffffu, c < 32 ? ba : bb, c & 31);
+                    if (!m_ok || n >= p.N) continue;
                     __half y;
                     if constexpr (kInt8) {
-                        // half(float(acc) * (float(s1[n]) * float(sx[m])))
-                        const float sc = __fmul_rn(s1f, sxf);
-                        y = __float2half_rn(__fmul_rn((float)(int32_t)r[c], sc));
+                        y = __float2half_rn(__fmul_rn((float)(int32_t)r[c], __fmul_rn(s1f, sxf)));
                         if (p.acc_dbg) p.acc_dbg[(size_t)m * p.N + n] = (int32_t)r[c];
                     } else {
                         y = __float2half_rn(__uint_as_float(r[c]));
@@ -252,20 +271,22 @@ __global__ void __launch_bounds__(kP2Threads, 1)
                     p.Y[(size_t)m * p.N + n] = y;
                 }
             };
-            float sx_a = load_sx32(m_tile * kP2Tokens), sx_b = load_sx32(m_tile * kP2Tokens + 32);
+            float s1_a = load_s1(n_base), s1_b = load_s1(n_base + 32);
             if (!mbar_wait(&tmem_full[b], (it >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * kP2Tokens);
-            // Few, large TMEM loads and a lean store loop: on M=8192, K=4096, N=14336 (int8) this kernel took
-            // 441 us with 16-column loads, 374 us with 64-column loads, 320 us once the common case dropped its
-            // per-element checks; the mainloop alone (no epilogue) runs in 280 us, and so does the kernel with
-            // the TMEM loads but no arithmetic or stores: the epilogue's instructions are what is left.
+            // Few, large TMEM loads and a lean store loop.  On M=8192, K=4096, N=14336 (int8), with the weight
+            // rows on the lanes, this kernel took 441 us with 16-column loads, 374 us with 64-column loads and
+            // 320 us once the common case dropped its per-element checks; the mainloop alone (no epilogue) runs
+            // in 280 us, and so does the kernel with the TMEM loads but no arithmetic or stores.  With tokens on
+            // the lanes and 16-byte stores it is still 320 us there (M=2048, K=N=4096: 43 -> 34 us): what is
+            // left is the output itself, 13 % more traffic through an L2 that the operand loads already fill.
 #pragma unroll 1
-            for (int c0 = 0; c0 < kP2Tokens; c0 += 64) {
-                const float s0 = sx_a, s1 = sx_b;
-                if (c0 + 64 < kP2Tokens) {
-                    sx_a = load_sx32(m_tile * kP2Tokens + c0 + 64);
-                    sx_b = load_sx32(m_tile * kP2Tokens + c0 + 96);
+            for (int c0 = 0; c0 < 256; c0 += 64) {
+                const float s0 = s1_a, s1 = s1_b;
+                if (c0 + 64 < 256) {
+                    s1_a = load_s1(n_base + c0 + 64);
+                    s1_b = load_s1(n_base + c0 + 96);
                 }
                 uint32_t r[64];
                 tmem_ld64(taddr + c0, r);

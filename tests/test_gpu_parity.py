@@ -191,10 +191,13 @@ def test_gemv_bias_and_fixture(kb):
 
 # ------------------------------------------------------------------ a11 W8A8
 GEMM_SHAPES = [(1, 128, 256), (5, 256, 64), (16, 512, 128), (33, 1152, 96), (16, 4096, 4096), (64, 4096, 1024),
-               (100, 4096, 4096), (128, 14336, 4096), (257, 3584, 512), (512, 4096, 4096), (1000, 4096, 1024)]
+               (100, 4096, 4096), (128, 14336, 4096), (257, 3584, 512), (512, 4096, 4096), (1000, 4096, 1024),
+               # CTA-pair kernel (M >= 512 and >= 74 tile pairs), ragged in M and N
+               (777, 1024, 9480)]
 
 
-@pytest.mark.parametrize('m,k,n', GEMM_SHAPES)
+# (1280, 512, 4100): CTA-pair kernel with N % 8 != 0, which takes its scalar stores
+@pytest.mark.parametrize('m,k,n', GEMM_SHAPES + [(1280, 512, 4100)])
 def test_w8a8_gemm_bit_exact(kb, m, k, n):
     _, ops, _ = kb
     x, _, res = case(m, k, n, seed=m)
