@@ -1,45 +1,44 @@
 // Per-token symmetric int8 activation quantization (path item a6).
 //
-// One CTA of 128 threads per token.  The token row is read from HBM once, kept in
-// registers across the block-wide amax reduction, and written back as int8: 2 bytes
-// read + 1 byte written per element, the algorithmic minimum.
+// One CTA of 256 threads per token.  The token row is read from HBM once (consecutive lanes read
+// consecutive 16-byte chunks), kept in registers across the block-wide amax reduction, and written back
+// as int8: 2 bytes read + 1 byte written per element, the algorithmic minimum.
 //
 // Arithmetic follows the reference's torch twin quantize_tensor_int8(x,'S',-1)
 // (kairos/quantization.py:111-141), not its fast-math CUDA kernel
 // (kernels/csrc/kairos_kernel/quant/quant_f16_to_i8.cu:46-86): fp32 amax clamped at
-// 1e-7, scale = amax/127 by IEEE division, q = rint(x/scale) by IEEE division and
-// round-half-even, sx = fp16(scale).
+// 1e-7, scale = amax/127 by IEEE division, q = rint(x/scale) with the IEEE quotient and
+// round-half-even (rint_div forms the quotient by division only next to a rounding boundary),
+// sx = fp16(scale).
 #include "common.cuh"
 
 namespace kairos {
 
-constexpr int kAqThreads = 128;
+constexpr int kAqThreads = 256;
 
-template <int R>   // 16-element chunks per thread, upper bound
+template <int R>   // 8-element chunks per thread, upper bound
 __global__ void __launch_bounds__(kAqThreads) act_quant_kernel(const __half* __restrict__ X,
                                                                int8_t* __restrict__ Xq,
                                                                __half* __restrict__ sx, int K) {
     chain_release();
     chain_wait();
     const int token = blockIdx.x;
-    const int chunks = K >> 4;
+    const int chunks = K >> 3;
     const uint4* row = reinterpret_cast<const uint4*>(X + (size_t)token * K);
-    uint4 v[R][2];
-    float amax = 0.f;
+    uint4 v[R];
+    __half2 hmax = __float2half2_rn(0.f);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * kAqThreads;
         if (c < chunks) {
-            v[r][0] = __ldcg(row + 2 * c);
-            v[r][1] = __ldcg(row + 2 * c + 1);
-            const __half2* h = reinterpret_cast<const __half2*>(&v[r][0]);
+            v[r] = __ldcg(row + c);
+            const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float2 f = __half22float2(h[i]);
-                amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-            }
+            for (int i = 0; i < 4; ++i) hmax = __hmax2(hmax, __habs2(h[i]));   // exact: the maximum of fp16 values
         }
     }
+    const float2 hm = __half22float2(hmax);
+    float amax = fmaxf(hm.x, hm.y);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     __shared__ float warp_max[kAqThreads / 32];
@@ -51,26 +50,27 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_kernel(const __half* __r
 
     const float scale = __fdiv_rn(fmaxf(amax, 1e-7f), 127.0f);
     if (threadIdx.x == 0) sx[token] = __float2half_rn(scale);
+    const float inv = __frcp_rn(scale);
 
-    uint4* out = reinterpret_cast<uint4*>(Xq + (size_t)token * K);
+    uint2* out = reinterpret_cast<uint2*>(Xq + (size_t)token * K);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * kAqThreads;
         if (c < chunks) {
-            const __half2* h = reinterpret_cast<const __half2*>(&v[r][0]);
-            uint32_t w[4];
+            const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+            uint32_t w[2];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 2; ++j) {
                 const float2 f0 = __half22float2(h[2 * j]);
                 const float2 f1 = __half22float2(h[2 * j + 1]);
-                const int q0 = __float2int_rn(__fdiv_rn(f0.x, scale));
-                const int q1 = __float2int_rn(__fdiv_rn(f0.y, scale));
-                const int q2 = __float2int_rn(__fdiv_rn(f1.x, scale));
-                const int q3 = __float2int_rn(__fdiv_rn(f1.y, scale));
+                const int q0 = rint_div(f0.x, scale, inv);
+                const int q1 = rint_div(f0.y, scale, inv);
+                const int q2 = rint_div(f1.x, scale, inv);
+                const int q3 = rint_div(f1.y, scale, inv);
                 w[j] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
                        ((uint32_t)(q3 & 0xff) << 24);
             }
-            out[c] = make_uint4(w[0], w[1], w[2], w[3]);
+            out[c] = make_uint2(w[0], w[1]);
         }
     }
 }
@@ -83,13 +83,15 @@ extern "C" int kairos_act_quant_i8(const void* X, void* Xq, void* sx, int M, int
     if (M == 0) return KAIROS_OK;
     if (!X || !Xq || !sx || ((uintptr_t)X & 15) || ((uintptr_t)Xq & 15) || ((uintptr_t)sx & 1))
         return KAIROS_ERR_ALIGN;
-    const int per_thread = (K / 16 + kAqThreads - 1) / kAqThreads;
+    const int per_thread = (K / 8 + kAqThreads - 1) / kAqThreads;
     const __half* x = static_cast<const __half*>(X);
     int8_t* q = static_cast<int8_t*>(Xq);
     __half* s = static_cast<__half*>(sx);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     cudaError_t e;
-    if (per_thread <= 2)
+    if (per_thread <= 1)
+        e = launch_chained(act_quant_kernel<1>, dim3(M), dim3(kAqThreads), 0, st, x, q, s, K);
+    else if (per_thread <= 2)
         e = launch_chained(act_quant_kernel<2>, dim3(M), dim3(kAqThreads), 0, st, x, q, s, K);
     else if (per_thread <= 4)
         e = launch_chained(act_quant_kernel<4>, dim3(M), dim3(kAqThreads), 0, st, x, q, s, K);

@@ -57,6 +57,22 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
 #endif
 
 // ---------------------------------------------------------------------------
+// rint(x / scale) with the result of IEEE division, without dividing in the common case.  x * (1/scale)
+// differs from the correctly rounded quotient by at most 3 * 2^-24 * |q| <= 2.3e-5 for |q| <= 127, so
+// both round to the same integer unless the product lies within 1e-4 of a rounding boundary (k + 0.5);
+// only then is the quotient formed by IEEE division (a dozen instructions) and rounded half-to-even.
+// Non-finite inputs take the division path as well.  `inv` = __frcp_rn(scale), once per token.
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ int rint_div(float x, float scale, float inv) {
+    const float r = __fmul_rn(x, inv);
+    const float t = rintf(r);
+    if (!(fabsf(r - t) <= 0.4999f)) return __float2int_rn(__fdiv_rn(x, scale));
+    return (int)t;
+}
+#endif
+
+// ---------------------------------------------------------------------------
 // uint4 unpack.  A 32-bit word of the base holds, for fixed (row, a, c), the
 // eight values k = 32a + 8b + 2c + d (b = nibble index within each 16-bit half,
 // d = which half).  unpack8 returns four half2, h[b] = (q[b,d=0], q[b,d=1]),

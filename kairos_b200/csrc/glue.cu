@@ -117,14 +117,14 @@ __device__ __forceinline__ float block_max_256(float v, float* scratch8) {
 
 // Per-token symmetric int8 quantization of 8 fp16 values held in a uint4, with the arithmetic of
 // act_quant_kernel (IEEE division, round-half-even): bit-identical to quantizing the stored fp16 tensor.
-__device__ __forceinline__ uint2 quant8(const uint4& v, float scale) {
+__device__ __forceinline__ uint2 quant8(const uint4& v, float scale, float inv) {
     const __half2* h = reinterpret_cast<const __half2*>(&v);
     uint32_t w[2];
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
         const float2 f0 = __half22float2(h[2 * j]), f1 = __half22float2(h[2 * j + 1]);
-        const int q0 = __float2int_rn(__fdiv_rn(f0.x, scale)), q1 = __float2int_rn(__fdiv_rn(f0.y, scale));
-        const int q2 = __float2int_rn(__fdiv_rn(f1.x, scale)), q3 = __float2int_rn(__fdiv_rn(f1.y, scale));
+        const int q0 = rint_div(f0.x, scale, inv), q1 = rint_div(f0.y, scale, inv);
+        const int q2 = rint_div(f1.x, scale, inv), q3 = rint_div(f1.y, scale, inv);
         w[j] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
                ((uint32_t)(q3 & 0xff) << 24);
     }
@@ -202,11 +202,12 @@ __global__ void __launch_bounds__(256) rms_norm_quant_kernel(__half* X, const __
     amax = block_max_256(amax, part);
     const float scale = __fdiv_rn(fmaxf(amax, 1e-7f), 127.0f);
     if (threadIdx.x == 0) sx[token] = __float2half_rn(scale);
+    const float inv_scale = __frcp_rn(scale);
     uint2* out = reinterpret_cast<uint2*>(Xq + (size_t)token * K);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * 256;
-        if (c < chunks) out[c] = quant8(v[r], scale);
+        if (c < chunks) out[c] = quant8(v[r], scale, inv_scale);
     }
 }
 
@@ -246,11 +247,12 @@ __global__ void __launch_bounds__(256) silu_mul_quant_kernel(const __half* __res
     amax = block_max_256(amax, part);
     const float scale = __fdiv_rn(fmaxf(amax, 1e-7f), 127.0f);
     if (threadIdx.x == 0) sx[token] = __float2half_rn(scale);
+    const float inv_scale = __frcp_rn(scale);
     uint2* out = reinterpret_cast<uint2*>(Xq + (size_t)token * I);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * 256;
-        if (c < chunks) out[c] = quant8(v[r], scale);
+        if (c < chunks) out[c] = quant8(v[r], scale, inv_scale);
     }
 }
 

@@ -75,6 +75,35 @@ def test_act_quant_bit_exact(kb, m, k):
     assert np.array_equal(bits(s.cpu().numpy()), bits(s_ref))
 
 
+def test_act_quant_rounding_boundaries(kb):
+    """Quotients on and next to the k + 0.5 rounding boundaries: rows whose scale is a power of two put
+    every half-integer quotient exactly on a tie (round half to even); rows with other scales put
+    quotients within a few ulp of a boundary, where only the correctly rounded IEEE quotient decides."""
+    _, ops, _ = kb
+    k = 512
+    rows = []
+    for amax in (127.0, 254.0, 63.5, 508.0):                 # scale 1, 2, 0.5, 4: x / scale = j + 0.5 exactly
+        sc = amax / 127.0
+        r = (np.arange(k, dtype=np.float32) % 250 - 125 + 0.5) * sc
+        r[0] = amax
+        rows.append(r)
+    rng = np.random.default_rng(3)
+    for amax in (100.0, 3.1, 777.0, 0.013, 41.7, 1999.0):    # near-boundary quotients under awkward scales
+        sc = np.float32(np.float16(amax)) / np.float32(127.0)
+        j = rng.integers(-126, 126, k).astype(np.float32) + 0.5
+        r = (j * sc).astype(np.float16).astype(np.float32)   # fp16 rounding scatters them around the boundary
+        r[0] = np.float16(amax)
+        rows.append(r)
+    x = np.stack(rows).astype(np.float16)
+    m = x.shape[0]
+    q = torch.empty((m, k), dtype=torch.int8, device='cuda')
+    s = torch.empty((m,), dtype=torch.float16, device='cuda')
+    ops.quant_fp16_to_int8(q, dev(x), s)
+    q_ref, s_ref = ko.act_quant(x)
+    assert np.array_equal(bits(s.cpu().numpy()), bits(s_ref))
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
 # ------------------------------------------------------------------ a7, a8, permute
 @pytest.mark.parametrize('path', SMALL, ids=[os.path.basename(p)[6:-4] for p in SMALL])
 def test_conversions_match_reference_fixtures(kb, path):
