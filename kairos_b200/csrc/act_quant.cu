@@ -8,7 +8,7 @@
 // (kairos/quantization.py:111-141), not its fast-math CUDA kernel
 // (kernels/csrc/kairos_kernel/quant/quant_f16_to_i8.cu:46-86): fp32 amax clamped at
 // 1e-7, scale = amax/127 by IEEE division, q = rint(x/scale) with the IEEE quotient and
-// round-half-even (rint_div forms the quotient by division only next to a rounding boundary),
+// round-half-even (quant8_chunk forms the quotient by division only next to a rounding boundary),
 // sx = fp16(scale).
 #include "common.cuh"
 
@@ -57,20 +57,7 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_kernel(const __half* __r
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * kAqThreads;
         if (c < chunks) {
-            const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
-            uint32_t w[2];
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const float2 f0 = __half22float2(h[2 * j]);
-                const float2 f1 = __half22float2(h[2 * j + 1]);
-                const int q0 = rint_div(f0.x, scale, inv);
-                const int q1 = rint_div(f0.y, scale, inv);
-                const int q2 = rint_div(f1.x, scale, inv);
-                const int q3 = rint_div(f1.y, scale, inv);
-                w[j] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
-                       ((uint32_t)(q3 & 0xff) << 24);
-            }
-            out[c] = make_uint2(w[0], w[1]);
+            out[c] = quant8_chunk(v[r], scale, inv);
         }
     }
 }

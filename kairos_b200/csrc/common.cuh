@@ -70,6 +70,41 @@ __device__ __forceinline__ int rint_div(float x, float scale, float inv) {
     if (!(fabsf(r - t) <= 0.4999f)) return __float2int_rn(__fdiv_rn(x, scale));
     return (int)t;
 }
+
+// Eight fp16 values -> eight int8 (two words), q = rint(x / scale) as above.  The product is rounded to an
+// integer by adding 1.5 * 2^23 (round-to-nearest-even of the fp32 adder); the low byte of the sum's bit
+// pattern is then q in two's complement (|q| <= 127), so no float-to-int conversion or masking is needed,
+// and one test per chunk sends a chunk with any quotient next to a rounding boundary (or a non-finite
+// value) to the exact divisions.
+__device__ __forceinline__ uint2 quant8_chunk(const uint4& v, float scale, float inv) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    const float magic = 12582912.f;
+    float x[8];
+    uint32_t u[8];
+    bool exact = false;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float r = __fmul_rn(x[i], inv);
+        const float s = __fadd_rn(r, magic);
+        const float t = __fadd_rn(s, -magic);
+        exact |= !(fabsf(__fadd_rn(r, -t)) <= 0.4999f);
+        u[i] = __float_as_uint(s);
+    }
+    if (exact) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) u[i] = (uint32_t)__float2int_rn(__fdiv_rn(x[i], scale));
+    }
+    uint2 out;
+    out.x = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
+    out.y = __byte_perm(__byte_perm(u[4], u[5], 0x0040), __byte_perm(u[6], u[7], 0x0040), 0x5410);
+    return out;
+}
 #endif
 
 // ---------------------------------------------------------------------------

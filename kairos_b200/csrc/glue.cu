@@ -117,19 +117,7 @@ __device__ __forceinline__ float block_max_256(float v, float* scratch8) {
 
 // Per-token symmetric int8 quantization of 8 fp16 values held in a uint4, with the arithmetic of
 // act_quant_kernel (IEEE division, round-half-even): bit-identical to quantizing the stored fp16 tensor.
-__device__ __forceinline__ uint2 quant8(const uint4& v, float scale, float inv) {
-    const __half2* h = reinterpret_cast<const __half2*>(&v);
-    uint32_t w[2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const float2 f0 = __half22float2(h[2 * j]), f1 = __half22float2(h[2 * j + 1]);
-        const int q0 = rint_div(f0.x, scale, inv), q1 = rint_div(f0.y, scale, inv);
-        const int q2 = rint_div(f1.x, scale, inv), q3 = rint_div(f1.y, scale, inv);
-        w[j] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
-               ((uint32_t)(q3 & 0xff) << 24);
-    }
-    return make_uint2(w[0], w[1]);
-}
+__device__ __forceinline__ uint2 quant8(const uint4& v, float scale, float inv) { return quant8_chunk(v, scale, inv); }
 
 __device__ __forceinline__ float absmax8(const uint4& v) {
     const __half2* h = reinterpret_cast<const __half2*>(&v);
