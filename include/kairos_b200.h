@@ -226,7 +226,10 @@ int kairos_switched_linear_q8(kairos_layer* layer, const void* Xq_i8, const void
 /* Convert ahead of use (e.g. on a side stream, one layer ahead): fills the cache entry the
  * given kernel id needs and returns; a later kairos_switched_linear on any stream waits for it. */
 int kairos_layer_prefetch(kairos_layer* layer, int comp_type, kairos_stream_t stream);
-/* Same call with HOST buffers: copies X in, runs, copies Y out, all on `stream`. */
+/* Same call with HOST buffers (pinned for the copies to be asynchronous).  X_host must hold its data when the
+ * call is made: the input copy runs on a stream of the context, so that it overlaps the previous call's
+ * compute and output copy, and is NOT ordered after earlier work on `stream`.  Y_host is complete once
+ * `stream` is synchronized.  Not for use inside a stream capture. */
 int kairos_switched_linear_host(kairos_layer* layer, const void* X_host, void* Y_host, int M, int comp_type,
                                 kairos_stream_t stream);
 

@@ -90,9 +90,15 @@ struct Ctx {
     size_t act_bytes = 0;
     void* gemm_ws = nullptr;     // split-K partial tiles
     size_t gemm_bytes = 0;
-    void* host_x = nullptr;      // device staging for the host-buffer entry point
+    // device staging for the host-buffer entry point: two input slots (the copy of call i+1 runs while call i
+    // computes), one output buffer, copies on the context's own streams
+    void* host_x[2] = {nullptr, nullptr};
     void* host_y = nullptr;
-    size_t host_x_bytes = 0, host_y_bytes = 0;
+    size_t host_x_bytes[2] = {0, 0}, host_y_bytes = 0;
+    cudaStream_t h2d = nullptr, d2h = nullptr;
+    cudaEvent_t x_ready[2] = {nullptr, nullptr}, x_free[2] = {nullptr, nullptr}, y_ready = nullptr, y_done = nullptr;
+    bool x_used[2] = {false, false};
+    unsigned host_calls = 0;
     cudaEvent_t fence = nullptr;
     std::mutex mu;
 };
@@ -353,8 +359,17 @@ void kairos_ctx_destroy(kairos_ctx* ctx) {
     cudaFree(c->transient);
     cudaFree(c->act_ws);
     cudaFree(c->gemm_ws);
-    cudaFree(c->host_x);
+    cudaFree(c->host_x[0]);
+    cudaFree(c->host_x[1]);
     cudaFree(c->host_y);
+    if (c->h2d) cudaStreamDestroy(c->h2d);
+    if (c->d2h) cudaStreamDestroy(c->d2h);
+    for (int i = 0; i < 2; ++i) {
+        if (c->x_ready[i]) cudaEventDestroy(c->x_ready[i]);
+        if (c->x_free[i]) cudaEventDestroy(c->x_free[i]);
+    }
+    if (c->y_ready) cudaEventDestroy(c->y_ready);
+    if (c->y_done) cudaEventDestroy(c->y_done);
     cudaEventDestroy(c->fence);
     cudaGetLastError();
     delete c;
@@ -467,11 +482,33 @@ int kairos_switched_linear_host(kairos_layer* layer, const void* X_host, void* Y
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const size_t xb = (size_t)M * L->K * 2, yb = (size_t)M * L->N * 2;
     int rc;
-    if ((rc = kairos::grow(&c->host_x, &c->host_x_bytes, xb)) != KAIROS_OK) return rc;
+    if (!c->h2d) {
+        KAIROS_CUDA_OK(cudaStreamCreateWithFlags(&c->h2d, cudaStreamNonBlocking));
+        KAIROS_CUDA_OK(cudaStreamCreateWithFlags(&c->d2h, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            KAIROS_CUDA_OK(cudaEventCreateWithFlags(&c->x_ready[i], cudaEventDisableTiming));
+            KAIROS_CUDA_OK(cudaEventCreateWithFlags(&c->x_free[i], cudaEventDisableTiming));
+        }
+        KAIROS_CUDA_OK(cudaEventCreateWithFlags(&c->y_ready, cudaEventDisableTiming));
+        KAIROS_CUDA_OK(cudaEventCreateWithFlags(&c->y_done, cudaEventDisableTiming));
+    }
+    const int slot = (int)(c->host_calls++ & 1u);
+    if ((rc = kairos::grow(&c->host_x[slot], &c->host_x_bytes[slot], xb)) != KAIROS_OK) return rc;
     if ((rc = kairos::grow(&c->host_y, &c->host_y_bytes, yb)) != KAIROS_OK) return rc;
-    KAIROS_CUDA_OK(cudaMemcpyAsync(c->host_x, X_host, xb, cudaMemcpyHostToDevice, st));
-    if ((rc = kairos::run_switched(L, c->host_x, c->host_y, M, comp_type, st)) != KAIROS_OK) return rc;
-    KAIROS_CUDA_OK(cudaMemcpyAsync(Y_host, c->host_y, yb, cudaMemcpyDeviceToHost, st));
+    // input copy on its own stream: it may run while the previous call still computes or copies out
+    if (c->x_used[slot]) KAIROS_CUDA_OK(cudaStreamWaitEvent(c->h2d, c->x_free[slot], 0));   // the call two back has read the slot
+    KAIROS_CUDA_OK(cudaMemcpyAsync(c->host_x[slot], X_host, xb, cudaMemcpyHostToDevice, c->h2d));
+    KAIROS_CUDA_OK(cudaEventRecord(c->x_ready[slot], c->h2d));
+    KAIROS_CUDA_OK(cudaStreamWaitEvent(st, c->x_ready[slot], 0));
+    if ((rc = kairos::run_switched(L, c->host_x[slot], c->host_y, M, comp_type, st)) != KAIROS_OK) return rc;
+    KAIROS_CUDA_OK(cudaEventRecord(c->x_free[slot], st));
+    c->x_used[slot] = true;
+    KAIROS_CUDA_OK(cudaEventRecord(c->y_ready, st));
+    // output copy on its own stream; `stream` waits for it, so the result is there once `stream` is synchronized
+    KAIROS_CUDA_OK(cudaStreamWaitEvent(c->d2h, c->y_ready, 0));
+    KAIROS_CUDA_OK(cudaMemcpyAsync(Y_host, c->host_y, yb, cudaMemcpyDeviceToHost, c->d2h));
+    KAIROS_CUDA_OK(cudaEventRecord(c->y_done, c->d2h));
+    KAIROS_CUDA_OK(cudaStreamWaitEvent(st, c->y_done, 0));
     return KAIROS_OK;
 }
 

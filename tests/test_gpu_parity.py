@@ -434,6 +434,27 @@ def test_host_buffer_entry_point(kb):
             assert_close(yh.numpy(), ref, 'host entry')
 
 
+def test_host_buffer_entry_point_calls_in_flight(kb):
+    """Twelve calls in a row with different inputs, sizes and output buffers and one synchronization at the
+    end: the input copy of a call overlaps the call before it, and every output is its own input's result."""
+    kairos_b200, _, _ = kb
+    from kairos_b200._lib import check, lib
+    _, w, res = case(1, 1024, 256, seed=70)
+    layer = _layer(kairos_b200, w)
+    st = torch.cuda.current_stream().cuda_stream
+    calls = []
+    for i in range(12):
+        m = (64, 512, 16, 300)[i % 4]
+        x, _ = ko.make_case(m, 1024, 4, seed=100 + i)
+        xh = torch.from_numpy(x.copy()).pin_memory()
+        yh = torch.zeros((m, 256), dtype=torch.float16).pin_memory()
+        calls.append((x, xh, yh))
+        check(lib.kairos_switched_linear_host(layer._native(), xh.data_ptr(), yh.data_ptr(), m, 2, st), 'host')
+    torch.cuda.synchronize()
+    for x, _, yh in calls:
+        assert np.array_equal(bits(yh.numpy()), bits(ko.forward(x, res, 2)))
+
+
 def test_side_stream_prefetch(kb):
     kairos_b200, _, _ = kb
     x, w, res = case(64, 512, 128, seed=60)
