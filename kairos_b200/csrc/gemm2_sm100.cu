@@ -81,6 +81,21 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                  : "memory");
 }
+// Tile order: bands of kP2Band token tiles; inside a band the token tile runs fastest, then the weight tile.
+// The clusters running at one time then share one band of activations (16 tiles = 4096 tokens, 16 MB of int8
+// at K = 4096) and a few weight tiles, and a band's activations stay in L2 while all weight tiles pass; with
+// the token tile running fastest over ALL of M, activations beyond the L2 size were re-read per weight tile.
+constexpr int kP2Band = 16;
+__device__ __forceinline__ void pair_tile_coords(int tile, int m_tiles, int n_tiles, int& m_tile, int& n_tile) {
+    const int per_band = kP2Band * n_tiles;
+    const int band = tile / per_band;
+    const int r = tile - band * per_band;
+    const int m0 = band * kP2Band;
+    const int width = m_tiles - m0 < kP2Band ? m_tiles - m0 : kP2Band;   // the last band may be narrower
+    n_tile = r / width;
+    m_tile = m0 + r - n_tile * width;
+}
+
 template <bool kInt8>
 __device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                           uint32_t accumulate) {
@@ -156,7 +171,8 @@ __global__ void __launch_bounds__(kP2Threads, 1)
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
-                const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+                int m_tile, n_tile;
+                pair_tile_coords(tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
                 const int row0 = is_w ? n_tile * 256 + (int)rank * kP2Rows : m_tile * kP2Tokens + (int)rank * 128;
                 for (int kb = 0; kb < p.kb_total; ++kb) {
                     if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
@@ -208,7 +224,8 @@ __global__ void __launch_bounds__(kP2Threads, 1)
         int it = 0;
         bool ok = true;
         for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++it) {
-            const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+            int m_tile, n_tile;
+            pair_tile_coords(tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
             const int m = m_tile * kP2Tokens + (int)rank * kP2Rows + row;
             const bool m_ok = m < p.M;
             const int n_base = n_tile * 256;
