@@ -490,8 +490,8 @@ def run_gpu_arm(args):
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
 # under profiles/ (same kernels, same shapes as the roofline points below); bytes.
 NCU_TRAFFIC = {
-    'umma_gemm_pair_kernel<int8> (cta_group::2, 256x256)': 111420928 + 200625408,   # profiles/umma_gemm_pair_int8_M8192_K4096_N14336.md
-    'umma_gemm_pair_kernel<f16> (cta_group::2, 256x256)': 926825984 + 223924992,    # profiles/umma_gemm_pair_f16_M8192_K4096_N14336.md
+    'umma_gemm_pair_kernel<int8> (cta_group::2, 256x256)': 152148992 + 191360768,   # profiles/umma_gemm_pair_int8_M8192_K4096_N14336.md
+    'umma_gemm_pair_kernel<f16> (cta_group::2, 256x256)': 372429056 + 216130304,    # profiles/umma_gemm_pair_f16_M8192_K4096_N14336.md
     'decode': 31219200,                                                              # profiles/decode_mma_M1_K4096_N14336.md
 }
 
