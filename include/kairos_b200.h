@@ -50,12 +50,15 @@ enum {
 int kairos_abi_version(void);
 const char* kairos_status_str(int status);
 const char* kairos_last_error(void);
-/* Status word the kernels raise when one of their bounded waits runs out (current device).
- * Read it after synchronising; clear != 0 resets it.  KAIROS_OK or KAIROS_ERR_DEVICE. */
+/* Status words the kernels raise when one of their bounded waits runs out (current device), including the
+ * word of kairos_w4a16_gemm_noalloc.  Read it after synchronising (the call itself synchronises the device
+ * once that entry has been used); clear != 0 resets it.  KAIROS_OK or KAIROS_ERR_DEVICE. */
 int kairos_device_status(int clear);
-/* Diagnostic (no counterpart in the reference): device buffer of 64 x 8 int64 that CTA 0 of the
- * tensor-core GEMMs fills with per-k-block clock64 stamps of its pipeline roles; null = off. */
-void kairos_debug_trace(void* device_buffer);
+/* Self-test of that mechanism (no counterpart in the reference): launches one CTA that waits, through the
+ * routine all pipeline kernels use, on a barrier nothing completes; the wait gives up after about a
+ * millisecond, raises the status word and the kernel returns.  After synchronising,
+ * kairos_device_status() reports KAIROS_ERR_DEVICE and the device remains usable. */
+int kairos_selftest_bounded_wait(kairos_stream_t stream);
 
 /* ---- primitive kernels -------------------------------------------------- */
 
@@ -82,21 +85,23 @@ int kairos_w4_to_f16(const void* qweight, const void* scales, const void* scaled
  * (kernels/csrc/kairos_kernel/trans_layout/trans_layout_marlin_c16_to_c8.cu:113-204). */
 int kairos_awq_to_qserve(const void* qweight, void* out_i8, int N, int K, kairos_stream_t stream);
 
-/* Y[M,N] = X[M,K] . dequant(W)^T (+bias), CUDA-core weight-streaming kernel, 1 <= M <= 32.
+/* Y[M,N] = X[M,K] . dequant(W)^T (+bias), CUDA-core weight-streaming kernel, 1 <= M <= 32; eight tokens
+ * share one pass over the weight, so M > 8 reads it ceil(M/8) times: it is the fallback for N % 8 == 4.
  * Replaces gemv_forward_cuda_new
  * (thirdparty/AWQ/kernels/csrc/quantization_new/gemv/gemv_cuda.cu:245-463). */
 int kairos_w4a16_gemv(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
                       const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, kairos_stream_t stream);
 
-/* Same product for 1 <= M <= 16 on warp-level tensor-core instructions: the uint4 values go from
- * registers straight into the MMA and the per-group factors are applied to the accumulators.  Serves
- * the batch sizes where the CUDA-core kernel above is instruction-bound.  Same reference counterpart
- * (gemv_cuda.cu:245-463, template cases Batch = 1..16). */
+/* Same product for 1 <= M <= 32 (N % 8 == 0) on warp-level tensor-core instructions: the packed weight is
+ * read once, by many small CTAs whose K slices meet through distributed shared memory (no scratch, one
+ * launch); the uint4 values go straight into the MMA and the per-group factors are applied to the
+ * accumulators.  Same reference counterpart (gemv_cuda.cu:245-463, template cases Batch = 1..16; the
+ * reference runs batch 17..32 through the same template). */
 int kairos_w4a16_decode(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
                         const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, kairos_stream_t stream);
 
-/* Kernel id 1 as the switched linear runs it: picks between the two kernels above by (M, N, K);
- * 1 <= M <= 32.  This is the drop-in for gemv_forward_cuda_new. */
+/* Kernel id 1 as the switched linear runs it: the decode kernel when N % 8 == 0, else the CUDA-core
+ * kernel; 1 <= M <= 32.  This is the drop-in for gemv_forward_cuda_new. */
 int kairos_w4a16_small_batch(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
                              const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, kairos_stream_t stream);
 

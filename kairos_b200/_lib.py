@@ -20,7 +20,7 @@ SIGNATURES = {
     'kairos_status_str': (c_char_p, [c_int]),
     'kairos_last_error': (c_char_p, []),
     'kairos_device_status': (c_int, [c_int]),
-    'kairos_debug_trace': (None, [c_void_p]),
+    'kairos_selftest_bounded_wait': (c_int, [c_void_p]),
     'kairos_act_quant_i8': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     'kairos_w4_to_w8': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     'kairos_w4_to_f16': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),

@@ -62,11 +62,13 @@ int* device_status_word() {
 }
 
 size_t gemm_workspace_bytes(int M, int N, int K);   // gemm_sm100.cu
+int noalloc_status(int clear);                       // gemm_sm100.cu: status word of kairos_w4a16_gemm_noalloc
 
 struct Lut {
     std::vector<int> bounds;   // exclusive right ends of the intervals, ascending
     std::vector<int> ids;
-    int memo_m = -1, memo_id = 0;
+    int memo_m = 0, memo_id = 0;
+    bool memo_valid = false;
 };
 
 struct CacheEntry {
@@ -75,8 +77,9 @@ struct CacheEntry {
     void* ptr = nullptr;
     size_t bytes = 0;
     uint64_t last_tick = 0;
-    cudaStream_t last_stream = nullptr;
-    cudaEvent_t ready = nullptr;   // recorded after the conversion that filled the entry
+    std::vector<cudaStream_t> users;   // every stream that was handed the pointer (its reads may still be queued)
+    cudaEvent_t ready = nullptr;       // recorded after the conversion that filled the entry
+    bool pinned = false;               // handed out while a stream was capturing: a graph holds the pointer
 };
 
 struct Ctx {
@@ -86,6 +89,7 @@ struct Ctx {
     std::vector<CacheEntry> entries;
     void* transient = nullptr;   // conversion target when the cache cannot hold the weight
     size_t transient_bytes = 0;
+    std::vector<cudaStream_t> transient_users;   // streams whose queued work may still read `transient`
     void* act_ws = nullptr;      // Xq [M,K] int8 followed by sx [M] fp16
     size_t act_bytes = 0;
     void* gemm_ws = nullptr;     // split-K partial tiles
@@ -109,8 +113,23 @@ struct Layer {
     const void *qweight, *scales, *scaled_zeros, *scales_to8, *scaled_zeros_to8, *scales_1, *bias;
 };
 
-static int grow(void** ptr, size_t* have, size_t need) {
+static bool capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return cs != cudaStreamCaptureStatusNone;
+}
+
+// Grows a library-owned buffer.  Growth frees and allocates (an implicit device synchronisation), which a
+// capturing stream must not see: inside a capture the buffers have to be large enough already
+// (kairos_ctx_reserve, or an eager call of the same shape before the capture).
+static int grow(void** ptr, size_t* have, size_t need, cudaStream_t st = nullptr, bool st_known = false) {
     if (*have >= need) return KAIROS_OK;
+    if (st_known && capturing(st))
+        return fail(KAIROS_ERR_WORKSPACE, "a library workspace would have to grow while the stream is capturing: call "
+                                          "kairos_ctx_reserve (or run the same shape eagerly) before the capture");
     if (*ptr) KAIROS_CUDA_OK(cudaFree(*ptr));   // cudaFree waits for work that may still use the block
     *ptr = nullptr;
     *have = 0;
@@ -124,69 +143,101 @@ static int grow(void** ptr, size_t* have, size_t need) {
 static int ensure_gemm_ws(Ctx* c, int M, int N, int K, cudaStream_t st) {
     const size_t need = gemm_workspace_bytes(M, N, K);
     if (c->gemm_bytes >= need) return KAIROS_OK;
-    (void)st;
-    return grow(&c->gemm_ws, &c->gemm_bytes, need);
+    return grow(&c->gemm_ws, &c->gemm_bytes, need, st, true);
 }
 
 static size_t act_ws_bytes(int M, int K) { return (((size_t)M * K + 255) & ~(size_t)255) + (size_t)M * 2 + 256; }
 
-// Make `st` wait for whatever `e.last_stream` had queued when the entry was last touched.
-static int order_after_last_use(Ctx* c, CacheEntry& e, cudaStream_t st) {
-    if (e.last_stream == st) return KAIROS_OK;
-    KAIROS_CUDA_OK(cudaEventRecord(c->fence, e.last_stream));
-    KAIROS_CUDA_OK(cudaStreamWaitEvent(st, c->fence, 0));
+// Make `st` wait for everything the streams in `users` (other than `st`) have queued so far.  Calls on a
+// context are serialised by its mutex, so whatever read the buffer has been enqueued by now.
+static int order_after_users(Ctx* c, const std::vector<cudaStream_t>& users, cudaStream_t st) {
+    for (cudaStream_t u : users) {
+        if (u == st) continue;
+        KAIROS_CUDA_OK(cudaEventRecord(c->fence, u));
+        KAIROS_CUDA_OK(cudaStreamWaitEvent(st, c->fence, 0));
+    }
     return KAIROS_OK;
 }
 
+static void note_user(std::vector<cudaStream_t>& users, cudaStream_t st) {
+    if (std::find(users.begin(), users.end(), st) == users.end()) users.push_back(st);
+}
+
 // Returns the converted weight of `layer` in `bits` precision, converting on a miss.
+// While `st` is capturing, nothing is evicted, freed or allocated: a miss fails with KAIROS_ERR_CACHE
+// (convert eagerly first, e.g. kairos_layer_prefetch), and an entry handed to a capture is pinned --
+// a graph may replay with its address -- until kairos_ctx_clear_cache.
 static int converted_weight(Layer* L, int bits, cudaStream_t st, const void** out) {
     Ctx* c = L->ctx;
     const size_t bytes = (size_t)L->N * L->K * (bits == 8 ? 1 : 2);
+    const bool cap = capturing(st);
     ++c->tick;
     for (auto& e : c->entries) {
         if (e.layer == L && e.bits == bits) {
             ++c->hits;
             e.last_tick = c->tick;
-            if (e.last_stream != st) KAIROS_CUDA_OK(cudaStreamWaitEvent(st, e.ready, 0));
-            e.last_stream = st;
+            if (std::find(e.users.begin(), e.users.end(), st) == e.users.end()) {
+                // first use on this stream: order it after the conversion.  A capturing stream can neither wait
+                // on an event recorded outside its capture nor let the host wait for it.
+                if (cap)
+                    return fail(KAIROS_ERR_CACHE, "the converted weight was produced on another stream and this stream is "
+                                                  "capturing: run the layer once on this stream before the capture");
+                KAIROS_CUDA_OK(cudaStreamWaitEvent(st, e.ready, 0));
+                e.users.push_back(st);
+            }
+            if (cap) e.pinned = true;
             *out = e.ptr;
             return KAIROS_OK;
         }
     }
+    if (cap)
+        return fail(KAIROS_ERR_CACHE, "the converted weight is not in the cache and the stream is capturing: conversions "
+                                      "allocate and evict, so run the layer (or kairos_layer_prefetch) eagerly before "
+                                      "the capture, with a cache that holds every layer the graph uses");
     ++c->misses;
     void* dst = nullptr;
     CacheEntry* slot = nullptr;
-    if (bytes <= c->cache_limit) {
+    size_t evictable = 0;
+    for (auto& e : c->entries)
+        if (!e.pinned) evictable += e.bytes;
+    if (bytes <= c->cache_limit && c->in_use - evictable + bytes <= c->cache_limit) {
         // evict least-recently-used entries until the new one fits; recycle an evicted block of the same size
-        while (c->in_use + bytes > c->cache_limit && !c->entries.empty()) {
-            size_t lru = 0;
-            for (size_t i = 1; i < c->entries.size(); ++i)
-                if (c->entries[i].last_tick < c->entries[lru].last_tick) lru = i;
+        while (c->in_use + bytes > c->cache_limit) {
+            size_t lru = c->entries.size();
+            for (size_t i = 0; i < c->entries.size(); ++i)
+                if (!c->entries[i].pinned && (lru == c->entries.size() || c->entries[i].last_tick < c->entries[lru].last_tick))
+                    lru = i;
+            if (lru == c->entries.size()) break;
             CacheEntry victim = c->entries[lru];
             c->entries.erase(c->entries.begin() + lru);
             c->in_use -= victim.bytes;
             ++c->evictions;
             if (!dst && victim.bytes == bytes) {
-                const int rc = order_after_last_use(c, victim, st);
+                const int rc = order_after_users(c, victim.users, st);
                 if (rc != KAIROS_OK) return rc;
                 dst = victim.ptr;
                 cudaEventDestroy(victim.ready);
             } else {
-                cudaFree(victim.ptr);
                 cudaEventDestroy(victim.ready);
+                KAIROS_CUDA_OK(cudaFree(victim.ptr));   // waits for the work that may still read the block
             }
         }
         if (!dst) KAIROS_CUDA_OK(cudaMalloc(&dst, bytes));
         CacheEntry e;
-        e.layer = L; e.bits = bits; e.ptr = dst; e.bytes = bytes; e.last_tick = c->tick; e.last_stream = st;
+        e.layer = L; e.bits = bits; e.ptr = dst; e.bytes = bytes; e.last_tick = c->tick;
+        e.users.push_back(st);
         KAIROS_CUDA_OK(cudaEventCreateWithFlags(&e.ready, cudaEventDisableTiming));
         c->entries.push_back(e);
         c->in_use += bytes;
         slot = &c->entries.back();
     } else {
-        // not cacheable: convert into the single reusable slot (stream-ordered reuse)
-        const int rc = grow(&c->transient, &c->transient_bytes, bytes);
+        // not cacheable: convert into the single reusable slot.  Its previous readers, on whatever stream,
+        // were enqueued under the context's mutex before this call, so fencing those streams orders the reuse.
+        int rc = order_after_users(c, c->transient_users, st);
         if (rc != KAIROS_OK) return rc;
+        if ((rc = grow(&c->transient, &c->transient_bytes, bytes)) != KAIROS_OK) return rc;
+        c->transient_users.clear();
+        c->transient_users.push_back(st);
         dst = c->transient;
     }
     int rc;
@@ -218,7 +269,7 @@ static int run_switched(Layer* L, const void* X, void* Y, int M, int comp, cudaS
         case KAIROS_COMP_W8A8: {
             const void* w8 = nullptr;
             if ((rc = converted_weight(L, 8, st, &w8)) != KAIROS_OK) return rc;
-            if ((rc = grow(&c->act_ws, &c->act_bytes, act_ws_bytes(M, L->K))) != KAIROS_OK) return rc;
+            if ((rc = grow(&c->act_ws, &c->act_bytes, act_ws_bytes(M, L->K), st, true)) != KAIROS_OK) return rc;
             if ((rc = ensure_gemm_ws(c, M, L->N, L->K, st)) != KAIROS_OK) return rc;
             void* xq = c->act_ws;
             void* sx = static_cast<uint8_t*>(c->act_ws) + (((size_t)M * L->K + 255) & ~(size_t)255);
@@ -271,21 +322,25 @@ const char* kairos_status_str(int status) {
 
 const char* kairos_last_error(void) { return kairos::g_last_error.c_str(); }
 
-/* Reads (and with clear != 0 resets) the device status word of the current device.  Call after
- * synchronising the stream(s) of interest.  KAIROS_OK or KAIROS_ERR_DEVICE. */
+/* Reads (and with clear != 0 resets) the status words of the current device: the host-mapped word the
+ * kernels raise, and the word inside the library image that launches of kairos_w4a16_gemm_noalloc raise
+ * (read with a plain copy, which synchronises the device).  Call after synchronising the stream(s) of
+ * interest.  KAIROS_OK or KAIROS_ERR_DEVICE. */
 int kairos_device_status(int clear) {
     int* w = kairos::device_status_word();
     if (!w) return KAIROS_ERR_CUDA;
-    const int v = *reinterpret_cast<volatile int*>(w);
+    int v = *reinterpret_cast<volatile int*>(w);
     if (clear) *reinterpret_cast<volatile int*>(w) = 0;
+    const int v2 = kairos::noalloc_status(clear);
+    if (v == KAIROS_OK) v = v2;
     return v;
 }
 
-/* Kernel id 1 (w4a16_gemv) is served by two kernels: the TMA-pipelined warp-MMA decode kernel up to
- * 16 tokens (N % 8 == 0), passes of the CUDA-core weight streamer otherwise (17..32 tokens, odd N). */
+/* Kernel id 1 (w4a16_gemv) is served by two kernels: the warp-MMA decode kernel (N % 8 == 0), the
+ * CUDA-core weight streamer otherwise (N % 8 == 4). */
 int kairos_w4a16_small_batch(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
                              const void* bias, void* Y, int M, int N, int K, kairos_stream_t stream) {
-    if (M <= 16 && (N % 8) == 0)
+    if (M <= 32 && (N % 8) == 0)
         return kairos_w4a16_decode(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, stream);
     return kairos_w4a16_gemv(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, stream);
 }
@@ -298,15 +353,15 @@ int kairos_lut_record(kairos_lut* t, int r, int comp_type) {
     if (!t) return KAIROS_ERR_ARG;
     Lut* l = reinterpret_cast<Lut*>(t);
     l->bounds.push_back(r + 1);   // interval (previous r, r] as a half-open [.., r+1)
-    l->ids.push_back(comp_type);
+    l->ids.push_back(comp_type);   // the memo is kept, as in lut.h: tables are filled before they are asked
     return KAIROS_OK;
 }
 
 int kairos_lut_get(kairos_lut* t, int m) {
     if (!t) return KAIROS_ERR_ARG;
     Lut* l = reinterpret_cast<Lut*>(t);
-    if (m == l->memo_m) return l->memo_id;   // one-entry memo: a layer asks again only when M changed
     if (l->ids.empty()) return KAIROS_ERR_ARG;
+    if (l->memo_valid && m == l->memo_m) return l->memo_id;   // one-entry memo: a layer asks again only when M changed
     int id;
     if (m >= l->bounds.back()) {
         id = l->ids.back();                  // beyond the last profiled M: keep the last winner
@@ -316,6 +371,7 @@ int kairos_lut_get(kairos_lut* t, int m) {
     }
     l->memo_m = m;
     l->memo_id = id;
+    l->memo_valid = true;
     return id;
 }
 

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/kairos_b200.h"
 
 namespace kairos {
@@ -26,6 +28,25 @@ int note_cuda_error(cudaError_t e);   // records the message, returns KAIROS_ERR
 int launch_status();                  // cudaGetLastError() -> status
 void set_last_error(const char* msg); // detail text returned by kairos_last_error()
 bool chained_launch_enabled();        // false when the environment sets KAIROS_NO_PDL=1
+
+// Function attributes belong to a device's context, so "already set" is tracked per device: a process that
+// drives several GPUs raises the dynamic shared-memory limit of a kernel once on each of them.
+struct PerDeviceFlag {
+    std::atomic<unsigned char> set[64];
+};
+template <typename Kernel>
+inline int ensure_dynamic_smem(PerDeviceFlag& flag, Kernel kernel, int bytes) {
+    int dev = 0;
+    const cudaError_t e0 = cudaGetDevice(&dev);
+    if (e0 != cudaSuccess) return note_cuda_error(e0);
+    if (dev < 0 || dev >= 64) return KAIROS_ERR_ARG;
+    if (!flag.set[dev].load(std::memory_order_acquire)) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return note_cuda_error(e);
+        flag.set[dev].store(1, std::memory_order_release);
+    }
+    return KAIROS_OK;
+}
 
 // ---------------------------------------------------------------------------
 // Programmatic dependent launch.  A kernel launched through launch_chained may become resident while the
@@ -112,6 +133,9 @@ __device__ __forceinline__ uint2 quant8_chunk(const uint4& v, float scale, float
 // eight values k = 32a + 8b + 2c + d (b = nibble index within each 16-bit half,
 // d = which half).  unpack8 returns four half2, h[b] = (q[b,d=0], q[b,d=1]),
 // i.e. two CONSECUTIVE k for each b.  All results are exact integers 0..15.
+// The magic-number idiom (or the nibble into the mantissa of 1024, then subtract, or scale by 1/16 and
+// subtract 64) is the one the wire format was designed for; the reference's form of it is
+// dequantize_s4_to_fp16x2, thirdparty/AWQ/kernels/csrc/quantization_new/dequantize.cuh:18-80.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void unpack8(uint32_t w, __half2 (&h)[4]) {
     // (w & 0x000f000f) | 0x64006400  ==  half2(1024 + q_lo, 1024 + q_hi)
@@ -213,7 +237,8 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t par
 // the common teardown.  The limit is ~2 s of polling; a healthy pipeline waits
 // microseconds.
 constexpr long long kWaitCycles = 4000000000LL;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                long long limit_cycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
@@ -221,11 +246,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         for (int i = 0; i < 16; ++i)
             if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitCycles) {
+        if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1;
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_limit(bar, parity, abort_flag, kWaitCycles);
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -362,11 +362,10 @@ int launch_gemm_pair(const void* X, const void* W, const __half* s1, const __hal
     p.acc_dbg = static_cast<int32_t*>(acc_dbg);
     p.status = device_status_word();
     if (!p.status) return KAIROS_ERR_CUDA;
-    static bool attr_set = false;
-    if (!attr_set) {
-        KAIROS_CUDA_OK(cudaFuncSetAttribute(umma_gemm_pair_kernel<kInt8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            kP2SmemBytes));
-        attr_set = true;
+    static PerDeviceFlag smem_attr;    // per instantiation
+    {
+        const int rc = ensure_dynamic_smem(smem_attr, umma_gemm_pair_kernel<kInt8>, kP2SmemBytes);
+        if (rc != KAIROS_OK) return rc;
     }
     int clusters = n_tiles * m_tiles;
     if (clusters > sms / 2) clusters = sms / 2;

@@ -56,11 +56,17 @@ struct GemmParams {
     long long* trace;            // diagnostic: per-k-block clock64 stamps of CTA 0 (null = off)
 };
 
+// Pipeline trace (build with -DKAIROS_TRACE): CTA 0 stamps clock64() per k block and role into p.trace.
+// Compiled out of the shipped library.
+#ifdef KAIROS_TRACE
 constexpr int kTraceSlots = 8;     // stamps per k block: see trace_stamp() call sites
 constexpr int kTraceBlocks = 64;   // k blocks recorded
 __device__ __forceinline__ void trace_stamp(const GemmParams& p, uint32_t i, int slot) {
     if (p.trace && blockIdx.x == 0 && i < kTraceBlocks) p.trace[i * kTraceSlots + slot] = clock64();
 }
+#else
+__device__ __forceinline__ void trace_stamp(const GemmParams&, uint32_t, int) {}
+#endif
 
 template <bool kInt8, int kMode, int BT>
 struct GemmCfg {
@@ -663,12 +669,8 @@ static int launch_one(const GemmArgs& a, const Plan& pl) {
     p.trace = g_trace;
     if (!p.status) return KAIROS_ERR_CUDA;
 
-    static bool attr_set = false;    // per instantiation
-    if (!attr_set) {
-        KAIROS_CUDA_OK(cudaFuncSetAttribute(umma_gemm_kernel<kInt8, kMode, BT>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set = true;
-    }
+    static PerDeviceFlag smem_attr;    // per instantiation
+    if ((rc = ensure_dynamic_smem(smem_attr, umma_gemm_kernel<kInt8, kMode, BT>, Cfg::kSmemBytes)) != KAIROS_OK) return rc;
     const int units = pl.n_tiles * pl.m_tiles * pl.splits;
     const int sms = device_sm_count();
     const int grid = units < sms ? units : sms;
@@ -732,11 +734,13 @@ template int launch_gemm<false, kModeW8>(const GemmArgs&);
 
 using kairos::GemmArgs;
 
-/* Diagnostic: when given a device buffer of 64 x 8 int64, CTA 0 of every tensor-core GEMM launched
+#ifdef KAIROS_TRACE
+/* Diagnostic build only: when given a device buffer of 64 x 8 int64, CTA 0 of every tensor-core GEMM launched
  * afterwards stamps clock64() per k block: [0] TMA issued, [1] MMA saw the stage, [2] MMA saw the
  * expanded operand, [3] MMA committed, [4..7] expander: saw the stage / loaded / got its slot /
  * published.  Null switches it off. */
 extern "C" void kairos_debug_trace(void* device_buffer) { kairos::g_trace = static_cast<long long*>(device_buffer); }
+#endif
 
 extern "C" size_t kairos_gemm_workspace_bytes(int M, int N, int K) { return kairos::gemm_workspace_bytes(M, N, K); }
 
@@ -780,10 +784,11 @@ extern "C" int kairos_f16_gemm(const void* X, const void* W16, const void* bias,
 // Allocation-free variant of the W4A16 tensor-core GEMM.
 //
 // Some hosts of this library may not allocate device memory at call time at all: an inference
-// server that hands the whole GPU to its own arena at start-up and forbids later cudaMalloc, a
-// real-time loop whose latency budget has no room for an allocator call, a plugin running inside
-// someone else's CUDA-graph capture.  For those callers the split-K scratch of the GEMM lives in a
-// fixed array inside the library image instead of a caller- or context-owned buffer.
+// server that hands the whole GPU to its own arena at start-up and forbids later cudaMalloc, or a
+// real-time loop whose latency budget has no room for an allocator call.  For those callers the
+// split-K scratch of the GEMM lives in a fixed array inside the library image instead of a caller- or
+// context-owned buffer.  The first call on a device resolves the array's address and sets kernel
+// attributes; make it outside any stream capture.
 //
 // The array is device memory that every GPU which loads the library keeps until the process ends.
 // Its name is only meaningful to device code; the host asks the runtime for its device address once
@@ -819,6 +824,27 @@ static int noalloc_slot(NoAllocSlot* out) {
     }
     *out = slot;
     return KAIROS_OK;
+}
+
+// Status word of the allocation-free entry on the current device: KAIROS_ERR_DEVICE after one of its
+// launches gave up on a bounded wait, else 0 (also when the entry was never used on this device).
+// Plain copies from and to the symbol's address: nothing is allocated.  Synchronises the device.
+int noalloc_status(int clear) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KAIROS_OK;
+    int* word = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        word = g_noalloc_slots[dev].status;
+    }
+    if (!word) return KAIROS_OK;
+    int v = 0;
+    KAIROS_CUDA_OK(cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (clear && v != 0) {
+        const int zero = 0;
+        KAIROS_CUDA_OK(cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    }
+    return v;
 }
 }  // namespace kairos
 

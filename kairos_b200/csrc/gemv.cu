@@ -9,11 +9,16 @@
 // the fp16 conversion does, multiplied with X in half2 over the 32-k chunk and
 // accumulated across chunks in fp32.  The 8 lanes of a weight row are reduced with
 // shuffles, the K slices of a block through shared memory.  No scratch memory, no atomics.
+// Up to eight tokens share one pass over the weight; more tokens take further passes (grid.y), so
+// beyond M = 8 this kernel is only the fallback for N % 8 == 4, which the warp-MMA decode kernel
+// (and the reference's own GEMV, gemv_cuda.cu:277) does not accept.
 //
 // Algorithmic bytes per call: K*N/2 (weights) + 4*(K/128)*N (factors) + 2*M*K + 2*M*N.
 #include "common.cuh"
 
 namespace kairos {
+
+int device_sm_count();   // gemm_sm100.cu
 
 constexpr int kGvThreads = 256;
 constexpr int kGvWarps = kGvThreads / 32;
@@ -131,7 +136,7 @@ extern "C" int kairos_w4a16_gemv(const void* X, const void* qweight, const void*
     int slices = 1;
     while (slices < kGvWarps && (steps + slices - 1) / slices > kGvUnroll) slices *= 2;
     const int n_rows = N / kInterleave;
-    while (slices < kGvWarps && (n_rows * slices) / kGvWarps < 2 * 148) slices *= 2;
+    while (slices < kGvWarps && (n_rows * slices) / kGvWarps < 2 * device_sm_count()) slices *= 2;
     const int steps_per_slice = (steps + slices - 1) / slices;
     const int rows_per_block = kGvWarps / slices;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

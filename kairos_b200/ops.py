@@ -89,7 +89,7 @@ def gemv_cuda_core(in_feats, kernel, scaling_factors, zeros, m, n, k, bias=None)
 
 
 def decode_forward(in_feats, kernel, scaling_factors, zeros, m, n, k, bias=None):
-    """W4A16 for 1 <= m <= 16 on the warp-level tensor-core decode kernel."""
+    """W4A16 for 1 <= m <= 32 on the warp-level tensor-core decode kernel."""
     x = in_feats.reshape(-1, k)
     out = torch.empty((m, n), dtype=torch.float16, device=x.device)
     with torch.cuda.device(x.device):

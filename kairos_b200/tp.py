@@ -11,6 +11,8 @@ its ``DynamicLinear`` and keeps that class as the per-rank compute.
 """
 from __future__ import annotations
 
+import time
+
 import torch
 import torch.distributed as dist
 
@@ -44,6 +46,77 @@ def shard_weight(weight, kind, rank, world):
         return weight[lo:hi, :].contiguous()
     lo, hi = shard_bounds(k, rank, world, 128)
     return weight[:, lo:hi].contiguous()
+
+
+class PeerLost(RuntimeError):
+    """A rank of the tensor-parallel group did not reach the step the others are about to run."""
+
+    def __init__(self, step, missing, waited_s):
+        super().__init__(f'ranks {missing} did not reach step {step} within {waited_s:.1f} s')
+        self.step, self.missing = step, missing
+
+
+class StepGuard:
+    """Host-side liveness check between steps of a tensor-parallel job.
+
+    A rank that died, hung in its own code or left the job is found out ON THE HOST, before the surviving
+    ranks enqueue the next collective: an all-reduce that a peer never joins cannot be recalled once it is
+    on the GPU.  Every rank publishes the number of the step it is about to run in the job's key-value store
+    (the store torch.distributed was initialised with: no GPU and no collective involved) and then waits,
+    with a limit, until all peers have published at least that number.  On a timeout it raises `PeerLost`;
+    the caller then stops launching work.  Ranks leave only between steps, with nothing in flight.
+
+    The second line of defence is the process group's own timeout: create the group with a short
+    ``timeout=`` (and, for NCCL, ``TORCH_NCCL_ASYNC_ERROR_HANDLING=1``, which makes torch's watchdog poll
+    ``ncclCommGetAsyncError`` and abort the communicator), so that a collective a peer never joins ends with
+    an error instead of blocking forever.  `collective_errors()` reports what that watchdog has seen.
+    """
+
+    def __init__(self, store, rank, world, timeout_s=5.0, prefix='kairos/step', poll_s=0.01):
+        self.store, self.rank, self.world = store, rank, world
+        self.timeout_s, self.prefix, self.poll_s = timeout_s, prefix, poll_s
+
+    def _key(self, r):
+        return f'{self.prefix}/{r}'
+
+    def arrive(self, step):
+        self.store.set(self._key(self.rank), str(int(step)))
+
+    def reached(self, r, step):
+        key = self._key(r)
+        if not self.store.check([key]):
+            return False
+        return int(self.store.get(key)) >= step
+
+    def wait_all(self, step):
+        """Publish `step` and return once every peer has; raise PeerLost after `timeout_s`."""
+        self.arrive(step)
+        t0 = time.monotonic()
+        pending = [r for r in range(self.world) if r != self.rank]
+        while pending:
+            pending = [r for r in pending if not self.reached(r, step)]
+            if not pending:
+                break
+            waited = time.monotonic() - t0
+            if waited > self.timeout_s:
+                raise PeerLost(step, pending, waited)
+            time.sleep(self.poll_s)
+
+    @staticmethod
+    def collective_errors(group=None):
+        """Asynchronous errors the backend's watchdog recorded for `group` (NCCL: the result of its
+        ncclCommGetAsyncError polling); an empty list when there are none or the backend keeps none."""
+        pg = group if group is not None else dist.distributed_c10d._get_default_group()
+        errs = []
+        try:
+            backend = pg._get_backend(torch.device('cuda')) if torch.cuda.is_available() else None
+            if backend is not None and hasattr(backend, 'get_error'):
+                e = backend.get_error()
+                if e is not None and 'NO_ERROR' not in str(e).upper() and 'SUCCESS' not in str(e).upper():
+                    errs.append(str(e))
+        except Exception:                 # a backend without error reporting is not an error of the job
+            pass
+        return errs
 
 
 class ColumnParallelLinear(torch.nn.Module):

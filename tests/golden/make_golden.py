@@ -13,7 +13,10 @@ extension modules, which are only touched by the GPU forward) and writes
   * ``config0_digests.json``  SHA-256 digests + sampled values of the full-size
                               M=16, K=N=4096 case (too large to commit whole),
   * ``lut_known_answers.json`` answers of the reference's C++ LUT class, compiled
-                              from its header, for the shipped Llama tables.
+                              from its header, for the shipped Llama tables,
+  * ``dequant_fn_n64_k384.npz`` output of the reference's own ``dequantize_tensor_awq``
+                              (thirdparty/AWQ/awq_method.py:105-116) on the per-(row, group)
+                              factors its ``from_module`` derives.
 
 The fixtures travel with the repository; the reference tree does not.
 """
@@ -116,6 +119,21 @@ def run_reference(dl, qz, awq, x16, w16, bias=None):
     return out
 
 
+def dequant_fn_fixture(dl, qz, awq, w16):
+    """W16 as the reference's dequantize_tensor_awq computes it.  The factors are re-derived with the
+    reference's own functions in the order of DynamicLinear.from_module (kairos/dynamic_linear.py:95-110):
+    int8 per row, uint4 per group of 128, scale_f = scale_2 * scale_1."""
+    w = torch.from_numpy(w16.copy())
+    n, k = w.shape
+    w8, cfg1 = qz.quantize_tensor_int8(w, max_int=127)
+    w4, cfg2 = dl.kairos_quantize_tensor_int4(w8, group_size=128)
+    scale_f = cfg2['scale_f'].view(n, -1) * cfg1['scale']
+    zero_f = cfg2['zero_pt_f'].view(n, -1)
+    w16_fn = awq.dequantize_tensor_awq(w4.clone().reshape(n, k), scale_f.reshape(n, -1), zero_f.reshape(n, -1), 128)
+    return {'W': w16, 'Q4': w4.reshape(n, k).to(torch.uint8).numpy(), 'scale_f': scale_f.numpy(),
+            'zero_f': zero_f.to(torch.float16).numpy(), 'W16_fn': w16_fn.reshape(n, k).numpy()}
+
+
 def digest(a):
     a = np.ascontiguousarray(a)
     return hashlib.sha256(a.tobytes()).hexdigest()
@@ -158,8 +176,22 @@ int main(int argc, char** argv) {
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+    if len(sys.argv) < 2 or not os.path.isdir(sys.argv[1]):
+        raise SystemExit('usage: make_golden.py <root of the reference source tree> [dequant_fn]')
+    ref_root = sys.argv[1]
     dl, qz, awq = import_reference(ref_root)
+
+    # the reference's dequantize_tensor_awq itself (one fixture; the small_* cases restate its mul_/add_)
+    _, w16 = make_case(1, 384, 64, seed=11)
+    fx = dequant_fn_fixture(dl, qz, awq, w16)
+    full = run_reference(dl, qz, awq, make_case(1, 384, 64, seed=11)[0], w16)
+    assert np.array_equal(fx['W16_fn'].view(np.uint16), full['W16'].view(np.uint16)), \
+        'dequantize_tensor_awq and the restated mul_/add_ disagree'
+    assert np.array_equal(fx['Q4'], full['Q4'])
+    np.savez_compressed(os.path.join(HERE, 'dequant_fn_n64_k384.npz'), **fx)
+    print('wrote dequant_fn fixture')
+    if len(sys.argv) > 2 and sys.argv[2] == 'dequant_fn':
+        return
 
     small = [  # (tag, M, K, N, seed, bias)
         ('n64_k256_m5', 5, 256, 64, 1, False),

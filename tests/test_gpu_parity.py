@@ -161,7 +161,12 @@ def test_gemv(kb, m, k, n):
 
 @pytest.mark.parametrize('m,k,n', [(1, 128, 256), (1, 4096, 4096), (2, 4096, 1024), (3, 1152, 96), (4, 14336, 4096),
                                    (5, 256, 64), (8, 4096, 14336), (9, 512, 128), (13, 3584, 512),
-                                   (16, 4096, 4096), (16, 18944, 3584)])
+                                   (16, 4096, 4096), (16, 18944, 3584),
+                                   # 17..32 tokens (four token tiles), one row block of a tile missing (N % 32 = 8, 24),
+                                   # every cluster size (1, 2, 4, 8 K slices) and both rows-per-warp variants
+                                   (17, 1024, 520), (24, 4096, 1024), (32, 4096, 4096), (32, 3584, 512), (31, 128, 40),
+                                   (6, 4096, 4104), (7, 2048, 8200), (12, 4096, 2072), (1, 28672, 8192), (2, 8192, 28672),
+                                   (8, 384, 1032), (3, 128, 8)])
 def test_decode_mma(kb, m, k, n):
     _, ops, _ = kb
     x, _, res = case(m, k, n, seed=m)
@@ -170,7 +175,7 @@ def test_decode_mma(kb, m, k, n):
     assert_close(y.cpu().numpy(), ko.y_w4a16(x, res), f'decode m={m} k={k} n={n}')
 
 
-@pytest.mark.parametrize('m,k,n', [(2, 4096, 6144), (1, 14336, 256), (12, 2048, 40)])
+@pytest.mark.parametrize('m,k,n', [(2, 4096, 6144), (1, 14336, 256), (12, 2048, 40), (27, 4096, 1024)])
 def test_decode_mma_launches_in_a_row_and_graph_replays(kb, m, k, n):
     """Launches in a row (each may start while its predecessor drains) and replays of a captured pair of
     launches all give the oracle's result."""
@@ -242,6 +247,22 @@ def test_w8a8_gemm_bit_exact(kb, m, k, n):
     assert np.array_equal(bits(y.cpu().numpy()), bits(y_ref)), 'scaled fp16 output'
 
 
+# The code path a production call takes: no accumulator dump, so the CTA-pair kernel runs its 16-byte-store
+# epilogue (shuffled activation scales, packed fp16 conversion) and the one-CTA kernel its check-free loop.
+@pytest.mark.parametrize('m,k,n', [(777, 1024, 9480), (1280, 512, 4100), (1024, 4096, 4096), (300, 512, 1024)])
+def test_w8a8_gemm_production_epilogue_bit_exact(kb, m, k, n):
+    _, ops, _ = kb
+    x, _, res = case(m, k, n, seed=m)
+    xq, sx = ko.act_quant(x)
+    w8 = ko.dequant_w8(res['qweight'], res['scales_to8'], res['scaled_zeros_to8'])
+    y = torch.empty((m, n), dtype=torch.float16, device='cuda')
+    ops.w8a8_gemm_forward_cuda(dev(xq), dev(w8), dev(res['scales_1']), dev(sx), y)
+    acc_ref = ko.acc_int32(xq, w8)
+    sc = res['scales_1'].astype(np.float32)[None, :] * sx.astype(np.float32)[:, None]
+    y_ref = (acc_ref.astype(np.float32) * sc).astype(np.float16)
+    assert np.array_equal(bits(y.cpu().numpy()), bits(y_ref)), 'scaled fp16 output without the accumulator dump'
+
+
 # ------------------------------------------------------------------ a10, a12, id 3
 @pytest.mark.parametrize('m,k,n', GEMM_SHAPES)
 def test_f16_gemms(kb, m, k, n):
@@ -298,7 +319,13 @@ def test_full_size_sampled_columns(kb, m, k, n):
     acc_ref = ko.acc_int32(xq, w8[cols])
     assert np.array_equal(acc.cpu().numpy()[:, cols], acc_ref)
     sc = res['scales_1'].astype(np.float32)[None, cols] * sx.astype(np.float32)[:, None]
-    assert np.array_equal(bits(y8.cpu().numpy()[:, cols]), bits((acc_ref.astype(np.float32) * sc).astype(np.float16)))
+    y8_ref = (acc_ref.astype(np.float32) * sc).astype(np.float16)
+    assert np.array_equal(bits(y8.cpu().numpy()[:, cols]), bits(y8_ref))
+    # the same product as a production call runs it (no accumulator dump: the vectorised store loop)
+    y8p = torch.empty((m, n), dtype=torch.float16, device='cuda')
+    ops.w8a8_gemm_forward_cuda(q, dev(w8), r['scales_1'], s, y8p)
+    assert np.array_equal(bits(y8p.cpu().numpy()[:, cols]), bits(y8_ref))
+    assert torch.equal(y8p, y8)
 
 
 # ------------------------------------------------------------------ module level

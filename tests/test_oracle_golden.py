@@ -43,6 +43,19 @@ def test_oracle_matches_reference_small(path):
     assert np.array_equal(bits(ko.y_w8a8(g['X'], res, bias)), bits(g['Y_w8a8']))
 
 
+def test_oracle_dequant_matches_reference_function():
+    """W16 as produced by the reference's own dequantize_tensor_awq
+    (thirdparty/AWQ/awq_method.py:105-116), called by the fixture generator."""
+    g = dict(np.load(os.path.join(os.path.dirname(__file__), 'golden', 'dequant_fn_n64_k384.npz')))
+    res = ko.from_module(g['W'])
+    assert np.array_equal(res['q4'], g['Q4'])
+    w16 = ko.dequant_w16(res['qweight'], res['scales'], res['scaled_zeros'])
+    assert np.array_equal(bits(w16), bits(g['W16_fn']))
+    # the per-(row, group) factors the function was given are the ones the resident tensors hold
+    n, k = g['W'].shape
+    assert np.array_equal(bits(res['scales'][:k // 128].T), bits(g['scale_f']))
+
+
 def test_oracle_matches_reference_config0():
     """M=16, K=N=4096, seed 0: digests of every tensor on the path."""
     dg = json.load(open(os.path.join(os.path.dirname(__file__), 'golden', 'config0_digests.json')))

@@ -96,3 +96,53 @@ def test_shard_rules():
         tp.shard_weight(w, 'row', 0, 8)           # 64-wide K shards would split a quantization group
     with pytest.raises(ValueError):
         tp.shard_weight(torch.zeros(20, 512), 'col', 0, 8)
+
+
+# ---------------------------------------------------------------------------- failure detection (host side)
+def _guard_worker(rank, world, port, out):
+    """Rank 1 runs step 1 and then never arrives at step 2 (it stays alive, idle: a rank hung in its own
+    code); rank 0 must learn that on the host within the limit, and a collective it starts anyway must end
+    with an error through the group's timeout."""
+    import datetime
+    import time
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    from kairos_b200 import tp
+    store = dist.distributed_c10d._get_default_store()
+    guard = tp.StepGuard(store, rank, world, timeout_s=1.0)
+    guard.wait_all(1)                                   # both ranks are there
+    y = torch.ones(4)
+    dist.all_reduce(y)
+    assert float(y[0]) == world
+    if rank == 1:
+        # never reaches step 2; leaves only after rank 0 has finished its checks
+        t0 = time.monotonic()
+        while not store.check(['kairos/test/done']) and time.monotonic() - t0 < 30:
+            time.sleep(0.05)
+        return
+    t0 = time.monotonic()
+    try:
+        guard.wait_all(2)
+        out['guard'] = 'no error'
+    except tp.PeerLost as e:
+        out['guard'] = ('lost', list(e.missing), e.step, time.monotonic() - t0)
+    # a collective the peer never joins: the short group timeout turns it into an error
+    t0 = time.monotonic()
+    try:
+        dist.all_reduce(torch.ones(4))
+        out['collective'] = 'no error'
+    except Exception as e:                               # noqa: BLE001 (backend-specific exception type)
+        out['collective'] = ('error', type(e).__name__, time.monotonic() - t0)
+    store.set('kairos/test/done', '1')
+
+
+def test_rank_that_never_arrives_is_detected_on_the_host():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_guard_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    kind, missing, step, waited = out['guard']
+    assert (kind, missing, step) == ('lost', [1], 2)
+    assert 0.9 < waited < 3.0
+    assert out['collective'][0] == 'error' and out['collective'][2] < 15.0
