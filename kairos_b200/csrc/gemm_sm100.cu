@@ -36,7 +36,7 @@ enum : int { kModeTma = 0, kModeW4 = 1, kModeW8 = 2 };
 constexpr int kTileN = 128;           // weight rows per tile (UMMA M)
 constexpr int kRowBytes = 128;        // K extent of one pipeline stage, in bytes of the MMA operand
 constexpr int kATileBytes = kTileN * kRowBytes;
-constexpr int kNumExpandWarps = 8;
+constexpr int kNumExpandWarps = 16;
 constexpr int kExpandGroups = 4;                                   // k blocks expanded concurrently
 constexpr int kExpandGroupWarps = kNumExpandWarps / kExpandGroups;
 constexpr int kSmemBudget = 224 * 1024;      // of the 227 KB a CTA may use; barriers and alignment slack come on top
@@ -62,7 +62,7 @@ struct GemmParams {
 constexpr int kTraceSlots = 8;     // stamps per k block: see trace_stamp() call sites
 constexpr int kTraceBlocks = 64;   // k blocks recorded
 __device__ __forceinline__ void trace_stamp(const GemmParams& p, uint32_t i, int slot) {
-    if (p.trace && blockIdx.x == 0 && i < kTraceBlocks) p.trace[i * kTraceSlots + slot] = clock64();
+    if (p.trace && blockIdx.x == 0 && i < kTraceBlocks && (threadIdx.x & 31) == 0) p.trace[i * kTraceSlots + slot] = clock64();
 }
 #else
 __device__ __forceinline__ void trace_stamp(const GemmParams&, uint32_t, int) {}
@@ -183,8 +183,11 @@ __device__ __forceinline__ UnitRange unit_range(const GemmParams& p, int unit) {
     u.tile = unit / p.splits;
     u.m_tile = u.tile % p.m_tiles;
     u.n_tile = u.tile / p.m_tiles;
-    u.kb0 = split * p.kb_per_split;
-    u.kb1 = min(p.kb_total, u.kb0 + p.kb_per_split);
+    // the stage bundles of K are dealt out as evenly as whole bundles allow (split i: bundles
+    // [i S / s, (i + 1) S / s) of S); kb_per_split holds the bundle size
+    const int bundles = p.kb_total / p.kb_per_split;
+    u.kb0 = (int)((long long)split * bundles / p.splits) * p.kb_per_split;
+    u.kb1 = (int)((long long)(split + 1) * bundles / p.splits) * p.kb_per_split;
     return u;
 }
 
@@ -362,7 +365,8 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
             // Token columns are read from TMEM in chunks of kChunk (large loads: the number of loads, not their
             // size, sets the time of the epilogue) and the activation scales of a chunk, one or two per lane,
             // are fetched one chunk ahead and handed round by shuffle.
-            constexpr int kChunk = BT >= 64 ? 64 : 16;
+            // (the dequantizing modes run 23 warps per CTA: their register budget allows 32 columns per load)
+            constexpr int kChunk = BT >= 64 ? (kExpand ? 32 : 64) : 16;
             const bool scaled = kInt8 && p.splits == 1;
             auto load_sx = [&](int m_first) {
                 const int m = m_first + lane;
@@ -382,6 +386,7 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                 }
                 uint32_t r[kChunk];
                 if constexpr (kChunk == 64) tmem_ld64(taddr + c0, r);
+                else if constexpr (kChunk == 32) tmem_ld32(taddr + c0, r);
                 else tmem_ld16(taddr + c0, r);
                 tmem_ld_wait();
                 if (p.splits == 1) {
@@ -532,6 +537,369 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------
+// W4A16 with the expanded weight operand in TENSOR MEMORY.
+//
+// In the kernel above the dequantized fp16 tile goes through shared memory: 16 KB written by the expander
+// warps and 16 KB read back by the tensor core for every 4 KB of packed weight, on top of the packed tile,
+// the activations and their reads.  At 128 bytes per clock the shared memory of an SM is then the bound
+// (about 450 cycles per 64-k block at BT = 64, measured with the pipeline trace), far below HBM speed.
+// Here the A operand of tcgen05.mma lives in tensor memory instead: an expander thread owns one weight
+// row of the tile (TMEM lane = row), dequantizes its 32 k of a k block in registers and stores them with
+// tcgen05.st into a ring of 32-column slots; the MMA reads A from that slot and only the activations (B)
+// from shared memory.  Shared-memory traffic per k block drops to the packed tile (4 KB in, 4 KB out) and
+// the activation tile.
+//
+//   warp 0      TMA producer: per stage (one quantization group = two k blocks) the packed tile
+//               [32 qweight rows][256 B], the group's scales / scaled zeros of the 128 rows, and the
+//               activations [2 k blocks][BT tokens][128 B] (128B-swizzled, the tcgen05 B operand)
+//   warp 1      MMA issuer, owner of the 512 TMEM columns: D (2 x BT fp32 columns, double-buffered) and
+//               the A ring (8 slots x 32 columns: 128 rows x 64 fp16)
+//   warps 2-5   epilogue (TMEM -> registers -> Y, or split-K partial tiles)
+//   warps 6-21  expanders: four groups of four warps (one per TMEM lane quarter); group g expands k
+//               blocks g, g + 4, ...
+// ---------------------------------------------------------------------------------
+template <int BT>
+struct W4Cfg {
+    static constexpr int kXTileBytes = BT * kRowBytes;                 // activations of one k block
+    static constexpr int kPackedBytes = 32 * 256;                      // [32 qweight rows][two k blocks x 128 B]
+    static constexpr int kFactorBytes = 1024;                          // scales at 0, scaled zeros at 256 (128 rows each)
+    static constexpr int kStageBytes = 2 * kXTileBytes + kPackedBytes + kFactorBytes;
+    static constexpr int kWTxBytes = kPackedBytes + 512;               // packed tile + scales + scaled zeros
+    static constexpr int kXTxBytes = 2 * kXTileBytes;
+    static constexpr int kStagesFit = kSmemBudget / kStageBytes;
+    static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
+    static constexpr int kASlots = 4;                                  // A ring in tensor memory: slots of one stage (64 columns)
+    static constexpr int kExpWarps = 16;
+    static constexpr int kFirstExpWarp = 8;
+    static constexpr int kWarps = kFirstExpWarp + kExpWarps;
+    static constexpr int kThreads = 32 * kWarps;
+    static constexpr int kTmemCols = 512;
+    // Successive MMAs into ONE accumulator tile wait for each other (about 90 cycles apiece at these small N,
+    // whatever N is); MMAs into different tiles overlap.  So the K steps of a tile go round-robin to kAcc
+    // accumulators, which the epilogue adds.
+    static constexpr int kAcc = BT <= 32 ? 4 : (BT <= 64 ? 2 : 1);
+    // One issuing thread needs 700-800 cycles per stage (waits, descriptors, eight MMAs, two commits: a chain
+    // of dependent instructions in a single thread), more than the expanders or the copies.  With two
+    // accumulators or more the stages therefore alternate between TWO issuer warps on different schedulers,
+    // each accumulating into its own tiles.
+    static constexpr int kIssuers = kAcc >= 2 ? 2 : 1;
+    static constexpr int kAccPerIssuer = kAcc / kIssuers;
+    static constexpr uint32_t kDCols = kAcc * BT;                      // columns of one (double-buffered) accumulator set
+    static constexpr uint32_t kAColBase = 2 * kDCols;                  // the A ring follows the two sets
+    static constexpr int kBarBytes = 8 * (2 * kStages + 2 * kASlots + 4) + 64;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;
+    static_assert(BT >= 32 && BT <= 128 && BT % 16 == 0, "token tile of the tensor-memory kernel");
+    static_assert(2 * kAcc * BT + kASlots * 64 <= 512, "accumulators and the A ring must fit the 512 TMEM columns");
+    // an expander warp that only OBSERVES a stage (another group owns it) must never fall two uses of a stage
+    // slot behind: the groups are at most kASlots stages apart
+    static_assert(kStages > kASlots, "stage ring shorter than the spread of the expander groups");
+    static_assert(kSmemBytes <= 227 * 1024, "exceeds the shared memory a CTA may use");
+    static constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(BT >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+};
+
+// D[tmem] (+)= A[tmem] . B[smem]^T, kind::f16, one CTA.
+__device__ __forceinline__ void umma_f16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 registers -> 16 consecutive 32-bit columns of the thread's TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int BT>
+__global__ void __launch_bounds__(W4Cfg<BT>::kThreads, 1)
+    w4a16_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                      const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_z,
+                      const GemmParams p) {
+    using Cfg = W4Cfg<BT>;
+    constexpr int kStages = Cfg::kStages;
+    constexpr int kASlots = Cfg::kASlots;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* stage_base = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+    uint64_t* full = bars;                       // stage filled by TMA
+    uint64_t* empty = full + kStages;            // stage released: its 4 expander warps + the MMAs that read its activations
+    uint64_t* a_full = empty + kStages;          // A slot written (4 expander warps)
+    uint64_t* a_empty = a_full + kASlots;        // A slot read by the MMAs (commit)
+    uint64_t* tmem_full = a_empty + kASlots;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 2);                     // the weight-side and the activation-side producer
+            mbar_init(&empty[s], 5);
+        }
+        for (int s = 0; s < kASlots; ++s) {
+            mbar_init(&a_full[s], 4);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], Cfg::kIssuers);
+            mbar_init(&tmem_empty[b], 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_x);
+        tma_prefetch_desc(&tmap_s);
+        tma_prefetch_desc(&tmap_z);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    chain_release();
+    chain_wait();
+
+    const int total_units = p.n_tiles * p.m_tiles * p.splits;
+
+    if (warp == 0) {
+        // ------------------------------ weight-side TMA producer -------------------
+        // (the whole warp walks the loop, one elected lane issues: see elect_one)
+        int s = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+            const UnitRange u = unit_range(p, unit);
+            for (int kb = u.kb0; kb < u.kb1; kb += 2) {
+                if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
+                uint8_t* wp = stage_base + s * Cfg::kStageBytes + 2 * Cfg::kXTileBytes;
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&full[s], Cfg::kWTxBytes);
+                    tma_load_2d(wp, &tmap_w, &full[s], kb * 64, u.n_tile * (kTileN / kInterleave));
+                    tma_load_2d(wp + Cfg::kPackedBytes, &tmap_s, &full[s], u.n_tile * kTileN, kb >> 1);
+                    tma_load_2d(wp + Cfg::kPackedBytes + 256, &tmap_z, &full[s], u.n_tile * kTileN, kb >> 1);
+                }
+                __syncwarp();
+                trace_stamp(p, (uint32_t)(kb - u.kb0), 0);
+                if (++s == kStages) { s = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 3) {
+        // ------------------------------ activation-side TMA producer ---------------
+        int s = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+            const UnitRange u = unit_range(p, unit);
+            for (int kb = u.kb0; kb < u.kb1; kb += 2) {
+                if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
+                uint8_t* st = stage_base + s * Cfg::kStageBytes;
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&full[s], Cfg::kXTxBytes);
+                    tma_load_3d(st, &tmap_x, &full[s], 0, u.m_tile * BT, kb);               // [2 k blocks][BT][128 B]
+                }
+                __syncwarp();
+                if (++s == kStages) { s = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1 || warp == 2) {
+        // ------------------------------ MMA issuers -------------------------------
+        // The whole warp walks the loop (every lane sees the same barriers and counters); one elected lane issues.
+        // Issuer `mi` takes the stages mi, mi + kIssuers, ... of the CTA's running stage count: with an even
+        // number of stage and A slots it meets every use of the slots it touches, so its parity waits stay valid.
+        const int mi = warp - 1;
+        if (mi < Cfg::kIssuers) {
+            static_assert(Cfg::kIssuers == 1 || (kStages % 2 == 0 && kASlots % 2 == 0), "issuers need even rings");
+            uint32_t i = 0;                              // running stage count of this CTA
+            int it = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++it) {
+                const UnitRange u = unit_range(p, unit);
+                const int b = it & 1;
+                if (!mbar_wait(&tmem_empty[b], ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)b * Cfg::kDCols + (uint32_t)(mi * Cfg::kAccPerIssuer * BT);
+                bool first = true;                       // this issuer's accumulators hold nothing of the tile yet
+                for (int kb = u.kb0; kb < u.kb1 && ok; kb += 2, ++i) {
+                    if ((int)(i % Cfg::kIssuers) != mi) continue;
+                    const int s = (int)(i % kStages), as = (int)(i % kASlots);
+                    const uint32_t phase = (i / kStages) & 1u, aphase = (i / kASlots) & 1u;
+                    if (!mbar_wait(&full[s], phase, abort_flag)) { ok = false; break; }
+                    trace_stamp(p, (uint32_t)(kb - u.kb0), 1);
+                    const uint8_t* st = stage_base + s * Cfg::kStageBytes;
+                    if (!mbar_wait(&a_full[as], aphase, abort_flag)) { ok = false; break; }
+                    trace_stamp(p, (uint32_t)(kb - u.kb0), 2);
+                    tc_fence_after();
+                    const uint32_t a_tmem = tmem_base + Cfg::kAColBase + (uint32_t)(as * 64);
+                    const uint64_t bdesc0 = umma_desc_sw128(smem_u32(st));
+                    const uint64_t bdesc1 = umma_desc_sw128(smem_u32(st + Cfg::kXTileBytes));
+                    if (elect_one()) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)   // K = 16 per instruction: 8 TMEM columns of A, 32 bytes of a B row
+                            umma_f16_a_tmem(d_tmem + (uint32_t)((j % Cfg::kAccPerIssuer) * BT), a_tmem + 8 * j,
+                                            (j < 4 ? bdesc0 : bdesc1) + 2 * (j & 3), Cfg::kIdesc,
+                                            (!first || j >= Cfg::kAccPerIssuer) ? 1u : 0u);
+                        umma_commit(&a_empty[as]);
+                        umma_commit(&empty[s]);
+                    }
+                    __syncwarp();
+                    first = false;
+                    trace_stamp(p, (uint32_t)(kb - u.kb0), 3);
+                }
+                if (ok) {
+                    // an issuer without a stage in this unit (a unit of one stage) has nothing to commit; the
+                    // epilogue leaves its accumulators out
+                    if (elect_one()) {
+                        if (first) mbar_arrive(&tmem_full[b]);
+                        else umma_commit(&tmem_full[b]);
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ------------------------------ epilogue ----------------------------------
+        const int q = warp & 3;                    // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;
+        int it = 0;
+        uint32_t i0 = 0;                           // running stage count at the start of the unit
+        bool ok = true;
+        for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++it) {
+            const UnitRange u = unit_range(p, unit);
+            const int n = u.n_tile * kTileN + row;
+            const bool n_ok = n < p.N;
+            const int b = it & 1;
+            const bool has_bias = p.bias != nullptr;
+            const __half bias_n = (has_bias && n_ok) ? __ldg(p.bias + n) : __float2half_rn(0.f);
+            // which issuers had a stage of this unit (stage i goes to issuer i % kIssuers)
+            const int unit_stages = (u.kb1 - u.kb0) / 2;
+            bool issued[Cfg::kIssuers];
+#pragma unroll
+            for (int mi = 0; mi < Cfg::kIssuers; ++mi)
+                issued[mi] = unit_stages >= Cfg::kIssuers || (unit_stages > 0 && (int)(i0 % Cfg::kIssuers) == mi);
+            i0 += (uint32_t)unit_stages;
+            if (!mbar_wait(&tmem_full[b], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)b * Cfg::kDCols;
+            uint32_t* part = p.partials + ((size_t)unit * BT) * kTileN + row;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BT; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c0, r);
+                tmem_ld_wait();
+                if (!issued[0]) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) r[c] = 0u;
+                }
+#pragma unroll
+                for (int a = 1; a < Cfg::kAcc; ++a) {       // the other accumulators of the set
+                    if (!issued[a / Cfg::kAccPerIssuer]) continue;
+                    uint32_t r2[32];
+                    tmem_ld32(taddr + a * BT + c0, r2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) + __uint_as_float(r2[c]));
+                }
+                if (p.splits == 1) {
+                    const int m0 = u.m_tile * BT + c0;
+                    if (n_ok) {
+                        __half* yp = p.Y + (size_t)m0 * p.N + n;
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            if (m0 + c < p.M) {
+                                __half y = __float2half_rn(__uint_as_float(r[c]));
+                                if (has_bias) y = __hadd(y, bias_n);
+                                yp[(size_t)c * p.N] = y;
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) part[(size_t)(c0 + c) * kTileN] = r[c];
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[b]);
+        }
+    } else if (warp >= Cfg::kFirstExpWarp) {
+        // ------------------------------ weight expanders --------------------------
+        // Thread = weight row of the tile (TMEM lane): 32 (warp % 4) + lane.  Its 64 k of a k block are 32 packed
+        // bytes: qweight row r >> 2, the k block's 128-byte line, 16-byte units 2 (r & 3) and 2 (r & 3) + 1
+        // (k 0..31 and 32..63 of the block).
+        const int grp = (warp - Cfg::kFirstExpWarp) >> 2;
+        const int row = 32 * (warp & 3) + lane;
+        const uint32_t w_off = (uint32_t)(2 * Cfg::kXTileBytes + (row >> 2) * 256 + ((row & 3) << 5));
+        const uint32_t f_off = (uint32_t)(2 * Cfg::kXTileBytes + Cfg::kPackedBytes + 2 * row);
+        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + Cfg::kAColBase;
+        uint32_t i = 0;                              // running stage count of this CTA
+        bool ok = true;
+        for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+            const UnitRange u = unit_range(p, unit);
+            for (int kb = u.kb0; kb < u.kb1; kb += 2, ++i) {
+                const int s = (int)(i % kStages), as = (int)(i % kASlots);
+                const uint32_t phase = (i / kStages) & 1u, aphase = (i / kASlots) & 1u;
+                // every warp observes every stage fill, in order (a parity wait is only valid one phase away)
+                if (!mbar_wait(&full[s], phase, abort_flag)) { ok = false; break; }
+                if ((int)(i & 3u) != grp) continue;
+                if ((warp & 3) == 0 && lane == 0) trace_stamp(p, (uint32_t)(kb - u.kb0), 4);
+                const uint8_t* st = stage_base + s * Cfg::kStageBytes;
+                uint4 raw[4];                                    // k 0..31, 32..63 of the first block, then of the second
+                raw[0] = *reinterpret_cast<const uint4*>(st + w_off);
+                raw[1] = *reinterpret_cast<const uint4*>(st + w_off + 16);
+                raw[2] = *reinterpret_cast<const uint4*>(st + w_off + 128);
+                raw[3] = *reinterpret_cast<const uint4*>(st + w_off + 144);
+                const __half2 sc = __half2half2(*reinterpret_cast<const __half*>(st + f_off));
+                const __half2 zc = __half2half2(*reinterpret_cast<const __half*>(st + f_off + 256));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);           // packed bytes and factors are in registers
+                if ((warp & 3) == 0 && lane == 0) trace_stamp(p, (uint32_t)(kb - u.kb0), 5);
+                if (!mbar_wait(&a_empty[as], aphase ^ 1, abort_flag)) { ok = false; break; }
+                if ((warp & 3) == 0 && lane == 0) trace_stamp(p, (uint32_t)(kb - u.kb0), 6);
+                tc_fence_after();
+                const uint32_t a_tmem = lane_base + (uint32_t)(as * 64);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    __half2 w[16];
+                    dequant_chunk32_fma(raw[c], sc, zc, w);      // 32 k, pairs in k order
+                    tmem_st16(a_tmem + 16 * c, *reinterpret_cast<const uint32_t(*)[16]>(w));
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[as]);
+                if ((warp & 3) == 0 && lane == 0) trace_stamp(p, (uint32_t)(kb - u.kb0), 7);
+            }
+        }
+    }
+
+    // ------------------------------ teardown --------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, KAIROS_ERR_DEVICE);
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);   // let copies that were already issued land
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
 int make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
@@ -575,6 +943,7 @@ int* device_status_word();   // api.cu: host-mapped word the kernels raise on a 
 
 static long long* g_trace = nullptr;   // diagnostic buffer of kTraceBlocks * kTraceSlots stamps, or null
 
+
 static int token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
 static int stage_bundle(int bt) { return bt <= 64 ? 4 : (bt == 128 ? 2 : 1); }   // GemmCfg::kSub
@@ -584,35 +953,46 @@ struct Plan {
     size_t partial_bytes;
 };
 
-static Plan make_plan(int M, int N, int K, bool int8) {
+// Split-K plan.  When a problem has fewer output tiles than the device has SMs, a tile's K range is cut
+// into runs of whole stage bundles, one CTA each, and a second pass sums the partial tiles.  Measured on
+// B200: with a tile for three SMs in four or more, the second pass and the partial traffic cost more than the
+// idle SMs, so only problems with fewer tiles than SMs are split.  The partial tiles
+// (tiles * splits * BT * 128 * 4 bytes) must fit `max_partial_bytes` (the caller's scratch, if bounded).
+// `w4_tmem` selects the geometry of the W4A16 kernel that keeps the expanded operand in tensor memory:
+// token tiles of 32..128 and stages of one quantization group.
+static Plan make_plan(int M, int N, int K, bool int8, size_t max_partial_bytes = ~(size_t)0, bool w4_tmem = false) {
     Plan pl;
     pl.bt = token_tile(M);
+    if (w4_tmem) pl.bt = pl.bt < 32 ? 32 : (pl.bt > 128 ? 128 : pl.bt);
     pl.n_tiles = (N + kTileN - 1) / kTileN;
     pl.m_tiles = (M + pl.bt - 1) / pl.bt;
-    const int sub = stage_bundle(pl.bt);
+    const int sub = w4_tmem ? 2 : stage_bundle(pl.bt);
     const int stages_total = (K / (int8 ? 128 : 64) + sub - 1) / sub;   // k blocks past K are zero-filled
     pl.kb_total = stages_total * sub;
+    pl.kb_per_split = sub;                                              // bundle size (see unit_range)
     const int tiles = pl.n_tiles * pl.m_tiles;
     const int sms = device_sm_count();
+    const size_t tile_bytes = (size_t)pl.bt * kTileN * 4;
     int splits = 1;
     if (tiles < sms) {
         splits = sms / tiles;
-        const int min_stages = 4 / sub;                                   // at least 4 k blocks per split
+        const int min_stages = 4 / sub > 0 ? 4 / sub : 1;                 // at least 4 k blocks per run
         const int max_by_k = stages_total / min_stages > 0 ? stages_total / min_stages : 1;
         if (splits > max_by_k) splits = max_by_k;
+        while (splits > 1 && (size_t)tiles * splits * tile_bytes > max_partial_bytes) --splits;
         if (splits < 1) splits = 1;
     }
-    const int stages_per_split = (stages_total + splits - 1) / splits;
-    pl.splits = (stages_total + stages_per_split - 1) / stages_per_split;
-    pl.kb_per_split = stages_per_split * sub;
-    pl.partial_bytes = pl.splits > 1 ? (size_t)tiles * pl.splits * pl.bt * kTileN * 4 : 0;
+    pl.splits = splits;
+    pl.partial_bytes = pl.splits > 1 ? (size_t)tiles * pl.splits * tile_bytes : 0;
     return pl;
 }
 
 size_t gemm_workspace_bytes(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    const Plan a = make_plan(M, N, K, false), b = make_plan(M, N, K, true);
-    return a.partial_bytes > b.partial_bytes ? a.partial_bytes : b.partial_bytes;
+    const Plan a = make_plan(M, N, K, false), b = make_plan(M, N, K, true),
+               c = make_plan(M, N, K, false, ~(size_t)0, M <= 128);
+    size_t need = a.partial_bytes > b.partial_bytes ? a.partial_bytes : b.partial_bytes;
+    return need > c.partial_bytes ? need : c.partial_bytes;
 }
 
 struct GemmArgs {
@@ -626,6 +1006,7 @@ struct GemmArgs {
     size_t workspace_bytes;
     cudaStream_t stream;
     int* status = nullptr;   // device word for timed-out waits; null = the per-device host-mapped word
+    size_t plan_cap = 0;     // upper bound of the split-K scratch the plan may use; 0 = the default bound
 };
 
 template <bool kInt8, int kMode, int BT>
@@ -687,6 +1068,50 @@ static int launch_one(const GemmArgs& a, const Plan& pl) {
     return launch_status();
 }
 
+template <int BT>
+static int launch_w4_tmem(const GemmArgs& a, const Plan& pl) {
+    using Cfg = W4Cfg<BT>;
+    CUtensorMap tw, tx, ts, tz;
+    int rc;
+    // qweight int16 [N/4, K]: 32 rows x 128 elements (two k blocks of the tile's 128 weight rows)
+    if ((rc = make_tmap_2d(&tw, a.W, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)a.N / kInterleave, (uint64_t)a.K, 128,
+                           32)) != KAIROS_OK) return rc;
+    // factors fp16 [K/128, N]: the tile's 128 rows of one group
+    if ((rc = make_tmap_2d(&ts, a.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.K / kGroup, (uint64_t)a.N,
+                           kTileN, 1)) != KAIROS_OK) return rc;
+    if ((rc = make_tmap_2d(&tz, a.scaled_zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)a.K / kGroup,
+                           (uint64_t)a.N, kTileN, 1)) != KAIROS_OK) return rc;
+    if ((rc = make_tmap_kblocks(&tx, a.X, false, (uint64_t)a.M, (uint64_t)a.K, BT, 2)) != KAIROS_OK) return rc;
+
+    GemmParams p;
+    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.n_tiles = pl.n_tiles; p.m_tiles = pl.m_tiles; p.splits = pl.splits;
+    p.kb_per_split = pl.kb_per_split; p.kb_total = pl.kb_total;
+    p.scales = a.scales; p.scaled_zeros = a.scaled_zeros; p.s1 = nullptr; p.sx = nullptr; p.bias = a.bias;
+    p.Y = static_cast<__half*>(a.Y);
+    p.acc_dbg = nullptr;
+    p.partials = static_cast<uint32_t*>(a.workspace);
+    p.status = a.status ? a.status : device_status_word();
+    p.trace = g_trace;
+    if (!p.status) return KAIROS_ERR_CUDA;
+    static PerDeviceFlag smem_attr;    // per instantiation
+    if ((rc = ensure_dynamic_smem(smem_attr, w4a16_tmem_kernel<BT>, Cfg::kSmemBytes)) != KAIROS_OK) return rc;
+    const int units = pl.n_tiles * pl.m_tiles * pl.splits;
+    const int sms = device_sm_count();
+    const int grid = units < sms ? units : sms;
+    cudaError_t e = launch_chained(w4a16_tmem_kernel<BT>, dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, a.stream, tw,
+                                   tx, ts, tz, p);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    if (pl.splits > 1) {
+        const int rc2 = launch_status();
+        if (rc2 != KAIROS_OK) return rc2;
+        e = launch_chained(splitk_reduce_kernel<false>, dim3(pl.n_tiles * pl.m_tiles * BT), dim3(kTileN), 0, a.stream, p,
+                           (int)BT);
+        if (e != cudaSuccess) return note_cuda_error(e);
+    }
+    return launch_status();
+}
+
 template <bool kInt8>
 int launch_gemm_pair(const void* X, const void* W, const __half* s1, const __half* sx, const __half* bias, void* Y,
                      void* acc_dbg, int M, int N, int K, cudaStream_t stream);   // gemm2_sm100.cu
@@ -713,9 +1138,21 @@ int launch_gemm(const GemmArgs& a) {
             if (rc != 1) return rc;
         }
     }
-    const Plan pl = make_plan(a.M, a.N, a.K, kInt8);
+    // W4A16: up to 128 tokens the kernel that keeps the expanded operand in tensor memory (its token tiles stop
+    // at 128); beyond, the shared-memory expander kernel with 256-token tiles
+    const bool w4_tmem = kMode == kModeW4 && a.M <= 128;
+    const Plan pl = make_plan(a.M, a.N, a.K, kInt8, a.plan_cap ? a.plan_cap : ~(size_t)0, w4_tmem);
     if (pl.partial_bytes > 0 && (!a.workspace || ((uintptr_t)a.workspace & 15) || a.workspace_bytes < pl.partial_bytes))
         return KAIROS_ERR_WORKSPACE;
+    if constexpr (kMode == kModeW4) {
+        if (w4_tmem) {
+            switch (pl.bt) {
+                case 32: return launch_w4_tmem<32>(a, pl);
+                case 64: return launch_w4_tmem<64>(a, pl);
+                default: return launch_w4_tmem<128>(a, pl);
+            }
+        }
+    }
     switch (pl.bt) {
         case 16: return launch_one<kInt8, kMode, 16>(a, pl);
         case 32: return launch_one<kInt8, kMode, 32>(a, pl);
@@ -855,7 +1292,11 @@ extern "C" int kairos_w4a16_gemm_noalloc(const void* X, const void* qweight, con
     if (!scales || !scaled_zeros) return KAIROS_ERR_ALIGN;
     if (M < 0 || N <= 0 || K <= 0 || (K % kGroup) != 0 || (N % 8) != 0) return KAIROS_ERR_SHAPE;
     if (M == 0) return KAIROS_OK;
-    const size_t need = make_plan(M, N, K, false).partial_bytes;
+    // The plan of the regular entry point when its scratch fits the built-in array; for M <= 64 otherwise a
+    // plan with fewer K runs that does fit; larger problems are rejected.
+    size_t need = make_plan(M, N, K, false, ~(size_t)0, M <= 128).partial_bytes;
+    if (need > KAIROS_NOALLOC_SCRATCH_BYTES && M <= 64)
+        need = make_plan(M, N, K, false, KAIROS_NOALLOC_SCRATCH_BYTES, true).partial_bytes;
     if (need > KAIROS_NOALLOC_SCRATCH_BYTES) {
         set_last_error("kairos_w4a16_gemm_noalloc: this (M, N, K) needs more split-K scratch than the 5 MiB built "
                        "into the library; use kairos_w4a16_gemm with a caller-owned workspace");
@@ -866,6 +1307,7 @@ extern "C" int kairos_w4a16_gemm_noalloc(const void* X, const void* qweight, con
     if (rc != KAIROS_OK) return rc;
     GemmArgs a{X, qweight, static_cast<const __half*>(scales), static_cast<const __half*>(scaled_zeros), nullptr,
                nullptr, static_cast<const __half*>(bias), Y, nullptr, M, N, K, slot.scratch,
-               (size_t)KAIROS_NOALLOC_SCRATCH_BYTES, reinterpret_cast<cudaStream_t>(stream), slot.status};
+               (size_t)KAIROS_NOALLOC_SCRATCH_BYTES, reinterpret_cast<cudaStream_t>(stream), slot.status,
+               (size_t)KAIROS_NOALLOC_SCRATCH_BYTES};
     return launch_gemm<false, kModeW4>(a);
 }

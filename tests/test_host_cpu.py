@@ -48,7 +48,7 @@ def test_argument_validation_needs_no_device():
     assert L.kairos_awq_to_qserve(16, 16, 48, 64, None) == -1             # N % 32
     assert L.kairos_switched_linear(None, 16, 16, 1, 0, None) == -8
     assert b'kernel id' in L.kairos_status_str(-6)
-    assert L.kairos_gemm_workspace_bytes(16, 4096, 4096) == 4 * 32 * 16 * 128 * 4     # 4 splits x 32 tiles
+    assert L.kairos_gemm_workspace_bytes(16, 4096, 4096) == 4 * 32 * 32 * 128 * 4     # 4 K runs x 32 tiles of 32 tokens
     assert L.kairos_gemm_workspace_bytes(8192, 4096, 4096) == 0
 
 
