@@ -2,6 +2,8 @@
 """TTFT / TPOT of a random-init decoder whose linears are switched linears (the reference's end-to-end latency benchmark: Llama-3-8B, Qwen2-7B, Llama-3-70B geometries).
 
     python bench_llm.py --model llama3-8b --batches 2,4,8,16,32 --prompt 1024 --new 512
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29511 \
+        bench_llm.py --model llama3-70b --batches 1,8,32,64           # tensor parallel, one rank per GPU
 
 Prints one JSON line per batch size: ttft_ms, tpot_ms, tokens_per_s, plus the LUT in use.  Protocol of
 the reference (utils/perf_eval.py:236-275): warm-up generations, TTFT = mean prefill + first token,
@@ -31,27 +33,43 @@ def main():
     args = ap.parse_args()
 
     import torch
+    import torch.distributed as dist
     import kairos_b200 as kb
     from kairos_b200 import llm, runtime
 
-    torch.cuda.set_device(0)
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    dev = f'cuda:{local}'
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', device_id=torch.device(dev))
+        dist.all_reduce(torch.zeros(1, device=dev))          # communicator set up before any capture
     cfg = llm.PRESETS[args.model]
-    ctx = runtime.Context('cuda:0', cache_bytes=int(args.cache_gb * (1 << 30)))
+    ctx = runtime.Context(dev, cache_bytes=int(args.cache_gb * (1 << 30)))
     kb.DynamicLinear.context = ctx
     t0 = time.perf_counter()
-    model = llm.Decoder(cfg, 'cuda:0', layers=args.layers, fuse_linears=not args.no_fuse, glue=args.glue)
+    model = llm.Decoder(cfg, dev, layers=args.layers, fuse_linears=not args.no_fuse, glue=args.glue,
+                        tp_rank=rank, tp_world=world)
     t_build = time.perf_counter() - t0
     t0 = time.perf_counter()
-    prof = llm.build_lut(model.linear_shapes(), cache=args.lut)
+    prof = llm.build_lut(model.linear_shapes(), device=dev, cache=args.lut)
     t_lut = time.perf_counter() - t0
+    if world > 1:
+        dist.barrier()
     lut = {str(s): [(r, name) for r, name, _ in prof.seg_perf_list[i]] for i, s in enumerate(prof.shape_list)}
-    print(json.dumps({'model': cfg.name, 'layers': len(model.model.layers), 'lut_seconds': round(t_lut, 1),
+    say = (lambda *a, **k: print(*a, **k)) if rank == 0 else (lambda *a, **k: None)
+    say(json.dumps({'model': model.cfg.name, 'tp': world, 'layers': len(model.model.layers), 'lut_seconds': round(t_lut, 1),
                       'build_seconds': round(t_build, 1), 'lut_mode': args.lut, 'lut': lut, 'fused_linears': not args.no_fuse, 'glue': args.glue,
                       'weights_gb': round(sum(b.numel() * b.element_size() for b in model.buffers()) / 2**30, 2)}))
     for b in [int(v) for v in args.batches.split(',')]:
         r = llm.measure_ttft_tpot(model, b, args.prompt, args.new)
-        r.update({'model': cfg.name, 'cache': ctx.stats(), 'peak_gb': round(torch.cuda.max_memory_allocated() / 2**30, 2)})
-        print(json.dumps(r), flush=True)
+        r.update({'model': model.cfg.name, 'tp': world, 'cache': ctx.stats(),
+                  'peak_gb': round(torch.cuda.max_memory_allocated() / 2**30, 2)})
+        say(json.dumps(r), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == '__main__':

@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
 
     // stage `s` <- group `grp`: rows and columns beyond the tensors arrive as zeros and count as bytes
     auto issue_weights = [&](int s, int grp) {
-        if (lane == 0) {
+        if (elect_one()) {
             uint8_t* st = ring + s * kStageBytes;
             mbar_arrive_expect_tx(&full[s], Cfg::kWBytes + Cfg::kFTx);
             tma_load_2d(st, &tmap_w, &full[s], grp * 256, row0 / 4);                       // bytes of the row, qweight row
@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
         }
     };
     auto issue_x = [&](int s, int grp) {
-        if (lane == 0) {
+        if (elect_one()) {
             mbar_arrive_expect_tx(&full[s], Cfg::kXBytes);
             tma_load_2d(ring + s * kStageBytes + Cfg::kWBytes, &tmap_x, &full[s], grp * kGroup, 0);   // k, token
         }

@@ -257,7 +257,8 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
 
     if (warp == 0) {
         // ------------------------------ weight-side TMA producer -------------------
-        if (lane == 0) {
+        // (the whole warp walks the loop, one elected lane issues: see elect_one)
+        {
             int s = 0;
             uint32_t phase = 0, ti = 0;
             bool ok = true;
@@ -266,6 +267,7 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                 for (int kb = u.kb0; kb < u.kb1; kb += kSub, ti += kSub) {
                     if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* st = stage_base + s * Cfg::kStageBytes;
+                    if (elect_one()) {
                     mbar_arrive_expect_tx(&full[s], Cfg::kWTxBytes);
                     if constexpr (kMode == kModeW4) {
                         // qweight [N/4, K] int16: 32 rows x (kSub x 64) columns
@@ -281,6 +283,8 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                         // operand tiles [k block][128 rows][128 B], swizzled
                         tma_load_3d(st, &tmap_w, &full[s], 0, u.n_tile * kTileN, kb);
                     }
+                    }
+                    __syncwarp();
                     trace_stamp(p, ti, 0);
                     if (++s == kStages) { s = 0; phase ^= 1; }
                 }
@@ -288,7 +292,7 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
         }
     } else if (warp == Cfg::kWarps - 1) {
         // ------------------------------ activation TMA producer --------------------
-        if (lane == 0) {
+        {
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -297,15 +301,19 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                 for (int kb = u.kb0; kb < u.kb1; kb += kSub) {
                     if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* st = stage_base + s * Cfg::kStageBytes + Cfg::kWStageBytes;
-                    mbar_arrive_expect_tx(&full[s], Cfg::kXStageBytes);
-                    tma_load_3d(st, &tmap_x, &full[s], 0, u.m_tile * BT, kb);   // [k block][BT rows][128 B]
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(&full[s], Cfg::kXStageBytes);
+                        tma_load_3d(st, &tmap_x, &full[s], 0, u.m_tile * BT, kb);   // [k block][BT rows][128 B]
+                    }
+                    __syncwarp();
                     if (++s == kStages) { s = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
+        // (the whole warp walks the loop, one elected lane issues)
+        {
             int s = 0, as = 0, it = 0;
             uint32_t phase = 0, aphase = 0, ti = 0;
             bool ok = true;
@@ -330,20 +338,25 @@ __global__ void __launch_bounds__(GemmCfg<kInt8, kMode, BT>::kThreads, 1)
                         const uint64_t adesc = umma_desc_sw128(a_addr);
                         const uint64_t bdesc =
                             umma_desc_sw128(smem_u32(st + Cfg::kWStageBytes + sub * Cfg::kXTileBytes));
+                        if (elect_one()) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)   // 4 x (K = 32 bytes) per 128-byte row; +2 = 32 bytes >> 4
-                            umma<kInt8>(d_tmem, adesc + 2 * j, bdesc + 2 * j, Cfg::kIdesc,
-                                        (kb + sub > u.kb0 || j > 0) ? 1u : 0u);
+                            for (int j = 0; j < 4; ++j)   // 4 x (K = 32 bytes) per 128-byte row; +2 = 32 bytes >> 4
+                                umma<kInt8>(d_tmem, adesc + 2 * j, bdesc + 2 * j, Cfg::kIdesc,
+                                            (kb + sub > u.kb0 || j > 0) ? 1u : 0u);
+                            if constexpr (kExpand) umma_commit(&a_empty[as]);
+                        }
+                        __syncwarp();
                         if constexpr (kExpand) {
-                            umma_commit(&a_empty[as]);
                             if (++as == kAStages) { as = 0; aphase ^= 1; }
                         }
                         trace_stamp(p, ti, 3);
                     }
-                    if (ok) umma_commit(&empty[s]);
+                    if (ok && elect_one()) umma_commit(&empty[s]);
+                    __syncwarp();
                     if (++s == kStages) { s = 0; phase ^= 1; }
                 }
-                if (ok) umma_commit(&tmem_full[b]);
+                if (ok && elect_one()) umma_commit(&tmem_full[b]);
+                __syncwarp();
             }
         }
     } else if (warp < 6) {

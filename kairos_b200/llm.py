@@ -15,6 +15,7 @@ import time
 from dataclasses import dataclass
 
 import torch
+import torch.distributed as dist
 import torch.nn.functional as F
 
 from . import ops
@@ -36,6 +37,21 @@ class DecoderConfig:
     rms_eps: float = 1e-5
     rope_theta: float = 500000.0
     qkv_bias: bool = False
+
+    def shard(self, world):
+        """This geometry as ONE rank of `world` tensor-parallel ranks sees it (Megatron split): the attention
+        heads, the KV heads and the MLP's inner channels are divided, the hidden size is not.  q|k|v and
+        gate|up become column-parallel (N / world), o and down row-parallel (K / world, one all-reduce each):
+        e.g. Llama-3-70B on 8 ranks runs (1280, 8192), (8192, 1024), (7168, 8192), (8192, 3584) per rank
+        with q|k|v and gate|up stacked."""
+        if world == 1:
+            return self
+        if self.n_heads % world or self.n_kv_heads % world or self.inter % (128 * world):
+            raise ValueError(f'{self.name} does not split over {world} ranks (heads {self.n_heads}/{self.n_kv_heads}, '
+                             f'inner size {self.inter}: every shard must keep whole heads and quantization groups)')
+        return DecoderConfig(f'{self.name}-tp{world}', self.layers, self.hidden, self.n_heads // world,
+                             self.n_kv_heads // world, self.head_dim, self.inter // world, self.vocab, self.rms_eps,
+                             self.rope_theta, self.qkv_bias)
 
     def linear_shapes(self):
         """Distinct (N, K) of the decoder linears, the key set of the profiler's LUT."""
@@ -129,8 +145,15 @@ class Decoder(torch.nn.Module):
     them as stock torch ops (what a HuggingFace model does)."""
 
     def __init__(self, cfg: DecoderConfig, device='cuda', seed=0, quant_strategy='DynamicLinear', layers=None,
-                 fuse_linears=True, glue='cuda'):
+                 fuse_linears=True, glue='cuda', tp_rank=0, tp_world=1, tp_group=None):
         super().__init__()
+        # Tensor parallelism (new; the reference is single-GPU): every rank builds the decoder of the SHARDED
+        # geometry -- its own heads and inner channels, quantized locally, with its own LUT -- and the outputs
+        # of the two row-parallel linears of a layer (o_proj, down_proj) are summed over the group with one
+        # all-reduce each.  Embedding, norms and lm_head are replicated (same seed on every rank).
+        self.full_cfg = cfg
+        self.tp_rank, self.tp_world, self.tp_group = tp_rank, tp_world, tp_group
+        cfg = cfg.shard(tp_world)
         self.cfg = cfg
         self.device = torch.device(device)
         self.fuse, self.glue = fuse_linears, glue
@@ -143,6 +166,8 @@ class Decoder(torch.nn.Module):
         self.lm_head = (torch.randn((cfg.vocab, cfg.hidden), generator=gen, device=self.device, dtype=torch.float32)
                         * 0.02).to(torch.float16)
         self.norm = RMSNorm(cfg.hidden, cfg.rms_eps, self.device)
+        if tp_world > 1:
+            gen = torch.Generator(device=self.device).manual_seed(seed + 1000 * (tp_rank + 1))   # the rank's own shards
         # build and quantize layer by layer so that at most one fp16 layer is alive
         for _ in range(n_layers):
             layer = DecoderLayer(cfg, self.device, fuse_linears)
@@ -203,6 +228,13 @@ class Decoder(torch.nn.Module):
             x.add_(delta)
         return mod(x)
 
+    def _reduce(self, y):
+        """Sum of a row-parallel linear's partial outputs over the tensor-parallel group (fp16, in place;
+        NCCL over NVLink, on the compute stream, so it is captured into the step's CUDA graph)."""
+        if self.tp_world > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.tp_group)
+        return y
+
     def _norm_then_linear(self, mod, x, delta, lin):
         """lin(norm(x + delta)); when the LUT sends this M to W8A8 the norm emits the int8 activations that
         kernel consumes, with no fp16 round trip."""
@@ -252,17 +284,17 @@ class Decoder(torch.nn.Module):
             o = F.scaled_dot_product_attention(q, kc[:, :, pos0:pos0 + s], vc[:, :, pos0:pos0 + s], is_causal=True,
                                                enable_gqa=True)
         o = o.transpose(1, 2).reshape(b, s, nh * d)
-        attn_out = a.o_proj(o)
+        attn_out = self._reduce(a.o_proj(o))
         m = layer.mlp
         if not self.fuse:
             h = self._norm(layer.post_attention_layernorm, x, attn_out)
-            return m.down_proj(F.silu(m.gate_proj(h)) * m.up_proj(h))
+            return self._reduce(m.down_proj(F.silu(m.gate_proj(h)) * m.up_proj(h)))
         gu = self._norm_then_linear(layer.post_attention_layernorm, x, attn_out, m.gate_up_proj)
         if self.glue == 'cuda' and self.fuse_quant and m.down_proj.wants_int8(b * s):
             aq, sa, _ = ops.silu_mul_quant(gu)
-            return m.down_proj.forward_q8(aq, sa)
+            return self._reduce(m.down_proj.forward_q8(aq, sa))
         act = ops.silu_mul(gu) if self.glue == 'cuda' else F.silu(gu[..., :cfg.inter]) * gu[..., cfg.inter:]
-        return m.down_proj(act)
+        return self._reduce(m.down_proj(act))
 
     def _stack(self, x, decode):
         """All layers, then the final norm (which carries the last residual addition)."""
