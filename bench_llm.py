@@ -69,6 +69,8 @@ def main():
                   'peak_gb': round(torch.cuda.max_memory_allocated() / 2**30, 2)})
         say(json.dumps(r), flush=True)
     if world > 1:
+        model.release_graphs()      # captured collectives must be gone before the group is destroyed
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -218,6 +218,16 @@ class Decoder(torch.nn.Module):
         self.graph = None
         self._prefill_graphs = {}
 
+    def release_graphs(self):
+        """Drop the captured CUDA graphs.  With tensor parallelism they hold the captured collectives, and a
+        process group must not be destroyed while such a graph is alive (its teardown then never returns):
+        call this, synchronize, and only then ``destroy_process_group``."""
+        import gc
+        self.graph = None
+        self._prefill_graphs = {}
+        gc.collect()
+        torch.cuda.synchronize(self.device)
+
     # ---- layers -----------------------------------------------------------------------------
     def _norm(self, mod, x, delta=None):
         """RMSNorm of the residual stream; a pending `delta` (output of the block before) is added to x in

@@ -71,3 +71,51 @@ def test_two_gpu_tensor_parallel_matches_per_shard_oracle():
         row = (parts[0].astype(np.float32) + parts[1].astype(np.float32)).astype(np.float16)
         bad, _ = ko.within_tolerance(out[f'row{m}'], row)
         assert bad == 0, f'row parallel m={m}'
+
+
+def _decoder_worker(rank, world, port, out):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    os.environ['NCCL_NVLS_ENABLE'] = '0'
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    dist.all_reduce(torch.zeros(1, device=dev))
+    import kairos_b200 as kb
+    from kairos_b200 import llm
+    cfg = llm.DecoderConfig('tiny', 2, 512, 8, 4, 64, 1024, 1000)
+    model = llm.Decoder(cfg, dev, layers=2, tp_rank=rank, tp_world=world)
+    assert model.cfg.n_heads == 4 and model.cfg.n_kv_heads == 2 and model.cfg.inter == 512
+    prof = kb.Profiler(model.linear_shapes())
+    prof.load_table({s: [(4, 'w4a16_gemv'), (16, 'w4a16_gemm'), (30720, 'w8a8')] for s in model.linear_shapes()})
+    kb.DynamicLinear.prof = prof
+    tokens = torch.randint(0, cfg.vocab, (2, 24), generator=torch.Generator(device=dev).manual_seed(3), device=dev)
+    model.allocate(2, 64)
+    eager = model.generate(tokens, 6, use_graph=False)
+    model.allocate(2, 64)
+    graphed = model.generate(tokens, 6, use_graph=True)      # the all-reduces are captured with the step
+    torch.cuda.synchronize()
+    gathered = [torch.empty_like(graphed) for _ in range(world)]
+    dist.all_gather(gathered, graphed)
+    if rank == 0:
+        out['eager'] = eager.cpu().numpy()
+        out['graphed'] = graphed.cpu().numpy()
+        out['ranks_agree'] = all(torch.equal(g, graphed) for g in gathered)
+        out['status'] = kb.runtime.device_status()
+    model.release_graphs()      # graphs with captured collectives must be gone before the group is destroyed
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_two_gpu_tensor_parallel_decoder_graph_matches_eager():
+    """A two-rank tensor-parallel decoder (sharded heads and inner channels, all-reduce after o_proj and
+    down_proj): the CUDA-graph path with the collectives captured gives the eager path's tokens, and every
+    rank ends with the same tokens."""
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_decoder_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert out['ranks_agree']
+    assert np.array_equal(out['eager'], out['graphed'])
+    assert out['status'] == 0
