@@ -190,7 +190,10 @@ static int converted_weight(Layer* L, int bits, cudaStream_t st, const void** ou
             return KAIROS_OK;
         }
     }
-    if (cap)
+    // A weight the cache cannot hold at all is converted into the reusable slot on every call; that is a
+    // plain kernel launch, so it may be captured -- provided the slot is already large enough.
+    const bool uncacheable = bytes > c->cache_limit;
+    if (cap && !(uncacheable && c->transient_bytes >= bytes))
         return fail(KAIROS_ERR_CACHE, "the converted weight is not in the cache and the stream is capturing: conversions "
                                       "allocate and evict, so run the layer (or kairos_layer_prefetch) eagerly before "
                                       "the capture, with a cache that holds every layer the graph uses");

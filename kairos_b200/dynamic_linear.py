@@ -152,15 +152,19 @@ class DynamicLinear(torch.nn.Module):
         return self._forward(input, m, self.comp_type).view(shape[0], shape[1], -1)
 
     @torch.no_grad()
-    def _forward(self, input: torch.Tensor, batch_token_len, comp_type) -> torch.Tensor:
-        """Run kernel `comp_type` on input [M, K] (or [..., K]) and return [M, N]."""
+    def _forward(self, input: torch.Tensor, batch_token_len, comp_type, out=None) -> torch.Tensor:
+        """Run kernel `comp_type` on input [M, K] (or [..., K]) and return [M, N] (written into `out`, a
+        contiguous fp16 [M, N] tensor, when given)."""
         x = input if input.dim() == 2 else input.reshape(-1, self.in_features)
         if x.dtype != torch.float16:
             x = x.to(torch.float16)
         if not x.is_contiguous():
             x = x.contiguous()
         m = x.shape[0]
-        out = torch.empty((m, self.out_features), dtype=torch.float16, device=x.device)
+        if out is None:
+            out = torch.empty((m, self.out_features), dtype=torch.float16, device=x.device)
+        elif out.shape != (m, self.out_features) or out.dtype != torch.float16 or not out.is_contiguous():
+            raise ValueError('out must be a contiguous fp16 [M, N] tensor')
         rc = _switched_linear(self._handle or self._native(), x.data_ptr(), out.data_ptr(), m, comp_type,
                               _raw_stream(x.device.index))
         if rc:
