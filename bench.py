@@ -265,7 +265,7 @@ def measure_int8_peak(torch, device):
         return {'int8_tops_measured': None, 'int8_source': f'unavailable ({type(exc).__name__})'}
 
 
-def timed_blocks(torch, dist, world, device, fn, steps, warmup, min_seconds=1.0, max_blocks=400):
+def timed_blocks(torch, dist, world, device, fn, steps, warmup, min_seconds=1.0, max_blocks=400, mark=False):
     """Device time of `steps` calls of fn, repeated as blocks until the timed region is at least `min_seconds`
     long (so that clock samples fall inside it); every block is bracketed by events, barrier + synchronize
     on both sides of the whole region, max over ranks.  Returns (median ms per step, all block values)."""
@@ -276,6 +276,8 @@ def timed_blocks(torch, dist, world, device, fn, steps, warmup, min_seconds=1.0,
         dist.barrier()
     torch.cuda.synchronize()
     blocks, t_start = [], time.perf_counter()
+    if mark:
+        torch.cuda.profiler.start()      # lets `ncu --profile-from-start off` see exactly the timed steps
     while len(blocks) < max_blocks and (not blocks or time.perf_counter() - t_start < min_seconds):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
@@ -285,6 +287,8 @@ def timed_blocks(torch, dist, world, device, fn, steps, warmup, min_seconds=1.0,
         e.synchronize()
         blocks.append(s.elapsed_time(e) / steps)
     torch.cuda.synchronize()
+    if mark:
+        torch.cuda.profiler.stop()
     if world > 1:
         dist.barrier()
         t = torch.tensor([statistics.median(blocks)], device=device)
@@ -457,7 +461,7 @@ def run_gpu_arm(args):
     if rank == 0:
         sampler.start()
     stats0 = ctx.stats()
-    ms_step, blocks = timed_blocks(torch, dist, world, device, step_fn, args.steps, args.warmup)
+    ms_step, blocks = timed_blocks(torch, dist, world, device, step_fn, args.steps, args.warmup, mark=True)
     stats1 = ctx.stats()
     clocks = sampler.stop() if rank == 0 else None
     n_timed_steps = len(blocks) * args.steps

@@ -1,6 +1,9 @@
-"""Run one kernel of the switched linear on seeded synthetic data (for profilers and quick timing).
+"""Time ONE kernel of the switched linear on seeded synthetic data: the single-kernel companion of bench.py.
 
-    python -m kairos_b200.run_case --kernel w8a8 --m 8192 --k 4096 --n 14336 --iters 3
+    python -m kairos_b200.bench_kernel --kernel w8a8 --m 8192 --k 4096 --n 14336 --iters 3
+
+Use it to compare a kernel before and after a change, or as the small fixed workload of a profiler capture
+(one kernel, a few launches, a few hundred MB on the device).
 
 Kernels: decode (kernel id 1), gemv (CUDA-core streamer), w4a16_gemm, w8a16_gemm, w8a8, fp16, act_quant,
 to_w8, to_f16.  Prints the mean device time per launch (CUDA events over `iters` launches after

@@ -214,7 +214,13 @@ def test_perf(proj_name, K, N, bias, m_grid=None, candidates=None, n=200, warmup
         for name in candidates:
             if m > 32 and 'gemv' in name:
                 continue
-            t = time_forward(layers, x, m, COMP_TYPE_NAME[name], n, warmup)
+            # one NVTX range per timed candidate (the reference marks its experiments the same way,
+            # test/test_asyn_trans.py:151,171): a timeline tool shows which kernels belong to which candidate
+            torch.cuda.nvtx.range_push(f'{proj_name} {name} m={m}')
+            try:
+                t = time_forward(layers, x, m, COMP_TYPE_NAME[name], n, warmup)
+            finally:
+                torch.cuda.nvtx.range_pop()
             table[m][name] = t
             if t < best_t:
                 best_t, best = t, name
