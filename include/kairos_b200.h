@@ -60,12 +60,32 @@ int kairos_device_status(int clear);
  * kairos_device_status() reports KAIROS_ERR_DEVICE and the device remains usable. */
 int kairos_selftest_bounded_wait(kairos_stream_t stream);
 
+/* ---- arithmetic rule of the three bit-exact stages ----------------------------------------
+ * The reference states activation quantization and the two weight conversions twice, and the two
+ * statements round differently:
+ *   KAIROS_ARITH_TORCH (default)  its torch functions (kairos/quantization.py:111-141,
+ *       thirdparty/AWQ/awq_method.py:105-116): scale = amax/127 and x/scale by IEEE division,
+ *       fp16(fp16(q*s) + sz) with two roundings;
+ *   KAIROS_ARITH_REFERENCE_CUDA   its CUDA kernels as nvcc --use_fast_math builds them
+ *       (kernels/setup.py:22): sx = fp16(amax / 127) and Xq = cvt.rni.sat.s8(x * (127 / amax)) with
+ *       approximate division and no clamp of amax (quant/quant_f16_to_i8.cu:54-77), and
+ *       fp16(q*s + sz) as ONE fused multiply-add (dequant_awq_format/dequant_i4_to_f16.cu:17-35,
+ *       dequant_i4_to_i8.cu:14-35,143-146).  Under this rule the three stages, and with them the
+ *       whole W8A8 path, return the bits the reference's own extension returns on the same GPU.
+ * The rule is process-wide, is read when a kernel is launched, and is part of the conversion cache's key.
+ * kairos_set_arithmetic returns the previous rule, or KAIROS_ERR_ARG.  The environment variable
+ * KAIROS_ARITHMETIC=reference_cuda selects the second rule at load time. */
+enum { KAIROS_ARITH_TORCH = 0, KAIROS_ARITH_REFERENCE_CUDA = 1 };
+int kairos_set_arithmetic(int rule);
+int kairos_get_arithmetic(void);
+
 /* ---- primitive kernels -------------------------------------------------- */
 
 /* Per-token symmetric int8 activation quantization: amax over K in fp32,
  * scale = max(amax,1e-7)/127 (IEEE division), Xq = rint(x/scale), sx = fp16(scale).
  * Replaces quant_fp16_to_int8 (kernels/csrc/kairos_kernel/quant/quant_f16_to_i8.cu:88-103)
- * with the arithmetic of its torch twin quantize_tensor_int8 (kairos/quantization.py:111-141). */
+ * with the arithmetic of its torch twin quantize_tensor_int8 (kairos/quantization.py:111-141), or, under
+ * KAIROS_ARITH_REFERENCE_CUDA, with the arithmetic of that kernel itself. */
 int kairos_act_quant_i8(const void* X_f16, void* Xq_i8, void* sx_f16, int M, int K, kairos_stream_t stream);
 
 /* uint4 base -> row-major int8 [N,K]: trunc(fp16(fp16(q*s)+sz)) with the *_to8 factors.

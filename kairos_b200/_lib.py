@@ -21,6 +21,8 @@ SIGNATURES = {
     'kairos_last_error': (c_char_p, []),
     'kairos_device_status': (c_int, [c_int]),
     'kairos_selftest_bounded_wait': (c_int, [c_void_p]),
+    'kairos_set_arithmetic': (c_int, [c_int]),
+    'kairos_get_arithmetic': (c_int, []),
     'kairos_act_quant_i8': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     'kairos_w4_to_w8': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     'kairos_w4_to_f16': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),

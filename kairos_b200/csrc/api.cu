@@ -20,6 +20,15 @@ int note_cuda_error(cudaError_t e) {
     return KAIROS_ERR_CUDA;
 }
 
+static std::atomic<int>& arithmetic_word() {
+    static std::atomic<int> rule([] {
+        const char* v = std::getenv("KAIROS_ARITHMETIC");
+        return (v && std::string(v) == "reference_cuda") ? (int)KAIROS_ARITH_REFERENCE_CUDA : (int)KAIROS_ARITH_TORCH;
+    }());
+    return rule;
+}
+int arithmetic_rule() { return arithmetic_word().load(std::memory_order_relaxed); }
+
 bool chained_launch_enabled() {
     static const bool on = [] {
         const char* e = getenv("KAIROS_NO_PDL");
@@ -74,6 +83,7 @@ struct Lut {
 struct CacheEntry {
     const void* layer = nullptr;
     int bits = 0;               // 8 or 16
+    int rule = 0;               // arithmetic rule the conversion ran under
     void* ptr = nullptr;
     size_t bytes = 0;
     uint64_t last_tick = 0;
@@ -171,9 +181,10 @@ static int converted_weight(Layer* L, int bits, cudaStream_t st, const void** ou
     Ctx* c = L->ctx;
     const size_t bytes = (size_t)L->N * L->K * (bits == 8 ? 1 : 2);
     const bool cap = capturing(st);
+    const int rule = arithmetic_rule();
     ++c->tick;
     for (auto& e : c->entries) {
-        if (e.layer == L && e.bits == bits) {
+        if (e.layer == L && e.bits == bits && e.rule == rule) {
             ++c->hits;
             e.last_tick = c->tick;
             if (std::find(e.users.begin(), e.users.end(), st) == e.users.end()) {
@@ -227,7 +238,7 @@ static int converted_weight(Layer* L, int bits, cudaStream_t st, const void** ou
         }
         if (!dst) KAIROS_CUDA_OK(cudaMalloc(&dst, bytes));
         CacheEntry e;
-        e.layer = L; e.bits = bits; e.ptr = dst; e.bytes = bytes; e.last_tick = c->tick;
+        e.layer = L; e.bits = bits; e.rule = rule; e.ptr = dst; e.bytes = bytes; e.last_tick = c->tick;
         e.users.push_back(st);
         KAIROS_CUDA_OK(cudaEventCreateWithFlags(&e.ready, cudaEventDisableTiming));
         c->entries.push_back(e);
@@ -324,6 +335,12 @@ const char* kairos_status_str(int status) {
 }
 
 const char* kairos_last_error(void) { return kairos::g_last_error.c_str(); }
+
+int kairos_set_arithmetic(int rule) {
+    if (rule != KAIROS_ARITH_TORCH && rule != KAIROS_ARITH_REFERENCE_CUDA) return KAIROS_ERR_ARG;
+    return kairos::arithmetic_word().exchange(rule);
+}
+int kairos_get_arithmetic(void) { return kairos::arithmetic_rule(); }
 
 /* Reads (and with clear != 0 resets) the status words of the current device: the host-mapped word the
  * kernels raise, and the word inside the library image that launches of kairos_w4a16_gemm_noalloc raise

@@ -28,6 +28,7 @@ int note_cuda_error(cudaError_t e);   // records the message, returns KAIROS_ERR
 int launch_status();                  // cudaGetLastError() -> status
 void set_last_error(const char* msg); // detail text returned by kairos_last_error()
 bool chained_launch_enabled();        // false when the environment sets KAIROS_NO_PDL=1
+int arithmetic_rule();                // KAIROS_ARITH_TORCH or KAIROS_ARITH_REFERENCE_CUDA (kairos_set_arithmetic)
 
 // Function attributes belong to a device's context, so "already set" is tracked per device: a process that
 // drives several GPUs raises the dynamic shared-memory limit of a kernel once on each of them.

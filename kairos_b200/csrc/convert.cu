@@ -17,7 +17,10 @@ namespace kairos {
 
 constexpr int kCvThreads = 256;
 
-template <bool kToInt8>
+// kFma selects the rounding of q*s + sz: false = product rounded, then sum rounded (the reference's torch
+// functions); true = one fused multiply-add, as in the reference's CUDA kernels
+// (dequant_awq_format/dequant_i4_to_f16.cu:17-35).
+template <bool kToInt8, bool kFma>
 __global__ void __launch_bounds__(kCvThreads) convert_kernel(const uint4* __restrict__ qweight,
                                                              const __half* __restrict__ scales,
                                                              const __half* __restrict__ scaled_zeros,
@@ -42,7 +45,10 @@ __global__ void __launch_bounds__(kCvThreads) convert_kernel(const uint4* __rest
     const __half2 s = __half2half2(__ldg(scales + (size_t)g * N + n));
     const __half2 z = __half2half2(__ldg(scaled_zeros + (size_t)g * N + n));
     __half2 w[16];
-    dequant_chunk32(raw, s, z, w);
+    if constexpr (kFma)
+        dequant_chunk32_fma(raw, s, z, w);
+    else
+        dequant_chunk32(raw, s, z, w);
     if constexpr (kToInt8) {
         // (int8) of an fp16 value truncates toward zero
         // (kernels/csrc/kairos_kernel/dequant_awq_format/dequant_i4_to_i8.cu:143-146)
@@ -115,8 +121,13 @@ static int launch_convert(const void* qweight, const void* s, const void* z, voi
     const long long tasks = (long long)(N / kInterleave) * kgroups;
     const int warps = kCvThreads / 32;
     const unsigned grid = (unsigned)((tasks + warps - 1) / warps);
-    convert_kernel<kToInt8><<<grid, kCvThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(qweight), static_cast<const __half*>(s), static_cast<const __half*>(z), out, N, K);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (arithmetic_rule() == KAIROS_ARITH_REFERENCE_CUDA)
+        convert_kernel<kToInt8, true><<<grid, kCvThreads, 0, st>>>(
+            static_cast<const uint4*>(qweight), static_cast<const __half*>(s), static_cast<const __half*>(z), out, N, K);
+    else
+        convert_kernel<kToInt8, false><<<grid, kCvThreads, 0, st>>>(
+            static_cast<const uint4*>(qweight), static_cast<const __half*>(s), static_cast<const __half*>(z), out, N, K);
     return launch_status();
 }
 

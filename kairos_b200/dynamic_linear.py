@@ -142,7 +142,8 @@ class DynamicLinear(torch.nn.Module):
         return super()._apply(fn, *args, **kwargs)
 
     # ---- forward ----------------------------------------------------------
-    @torch.no_grad()
+    # forward / _forward / forward_q8 pass raw pointers to the library and build no autograd graph; they carry
+    # no torch.no_grad() wrapper because entering one costs about as much host time as the launch itself
     def forward(self, input: torch.Tensor) -> torch.Tensor:
         shape = input.shape
         m = input.numel() // shape[-1]
@@ -151,7 +152,6 @@ class DynamicLinear(torch.nn.Module):
             self.comp_type = type(self).prof.get_comp_type(self.shape, m)
         return self._forward(input, m, self.comp_type).view(shape[0], shape[1], -1)
 
-    @torch.no_grad()
     def _forward(self, input: torch.Tensor, batch_token_len, comp_type, out=None) -> torch.Tensor:
         """Run kernel `comp_type` on input [M, K] (or [..., K]) and return [M, N] (written into `out`, a
         contiguous fp16 [M, N] tensor, when given)."""
@@ -180,7 +180,6 @@ class DynamicLinear(torch.nn.Module):
             self.comp_type = type(self).prof.get_comp_type(self.shape, m)
         return self.comp_type == COMP_TYPE_NAME['w8a8']
 
-    @torch.no_grad()
     def forward_q8(self, xq, sx):
         """W8A8 on activations that are already quantized: xq int8 [..., K], sx fp16 [tokens] -> [..., N]."""
         m = xq.numel() // self.in_features

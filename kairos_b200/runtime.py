@@ -79,6 +79,38 @@ def device_status(clear=True):
     return lib.kairos_device_status(1 if clear else 0)
 
 
+ARITHMETIC = {'torch': 0, 'reference_cuda': 1}
+
+
+def set_arithmetic(rule):
+    """Select the arithmetic of activation quantization and the two weight conversions, process-wide:
+    'torch' (default; the reference's torch functions: IEEE division, product and sum rounded separately)
+    or 'reference_cuda' (the reference's CUDA kernels as its build compiles them: approximate division, one
+    fused multiply-add; bit-identical to its extension on the same GPU).  Returns the previous rule's name."""
+    prev = lib.kairos_set_arithmetic(ARITHMETIC[rule])
+    check(prev, 'kairos_set_arithmetic')
+    return {v: k for k, v in ARITHMETIC.items()}[prev]
+
+
+def get_arithmetic():
+    return {v: k for k, v in ARITHMETIC.items()}[lib.kairos_get_arithmetic()]
+
+
+class arithmetic:
+    """``with runtime.arithmetic('reference_cuda'): ...`` -- the rule inside the block, restored after it."""
+
+    def __init__(self, rule):
+        self.rule = rule
+
+    def __enter__(self):
+        self.prev = set_arithmetic(self.rule)
+        return self
+
+    def __exit__(self, *exc):
+        set_arithmetic(self.prev)
+        return False
+
+
 _gemm_ws = {}
 
 

@@ -8,7 +8,10 @@ leg of the benchmark may import it.  The shipped package never does.
 Parity status: PINNED against outputs of the reference's own Python functions,
 generated in a container that holds the reference sources and committed as
 ``tests/golden/*.npz`` / ``tests/golden/config0_digests.json`` (generator:
-``tests/golden/make_golden.py``).  The reference's own tests pin only the
+``tests/golden/make_golden.py``); the ``*_cuda`` functions, which restate the
+reference's CUDA kernels where those round differently from its torch functions,
+are pinned against outputs of the reference's own extension run on a B200
+(``tests/golden/ref_cuda_*.npz``, generator ``tests/golden/make_golden_cuda.py``).  The reference's own tests pin only the
 AWQ->QServe nibble permutation (``test/test_trans_layout.py:46-52``) and the
 pack/unpack round trip (``test/depacking.py``); both are restated here too.
 
@@ -184,6 +187,61 @@ def dequant_w8(qweight, scales_to8, scaled_zeros_to8):
     """
     v = dequant_w16(qweight, scales_to8, scaled_zeros_to8).astype(np.float32)
     return np.trunc(v).astype(np.int8)
+
+
+# --------------------------------------------------------------------------
+# the same three stages as the reference's CUDA kernels compute them
+# --------------------------------------------------------------------------
+def dequant_w16_cuda(qweight, scales, scaled_zeros):
+    """uint4 base -> fp16 weight with ONE rounding: fp16(q*s + sz), the ``__hfma2`` of
+    kernels/csrc/kairos_kernel/dequant_awq_format/dequant_i4_to_f16.cu:17-35.  q*s + sz is exact in
+    fp64 (4 + 11 significant bits times 11, exponents within fp16's range), and numpy converts fp64 to
+    fp16 with a single correct rounding.  Pinned by ``tests/golden/ref_cuda_*.npz``, outputs of the
+    reference's own extension built for sm_100a and run on a B200."""
+    q = unpack_awq(qweight)
+    n, k = q.shape
+    exact = (q.astype(np.float64) * _expand_groups(scales, n, k).astype(np.float64)
+             + _expand_groups(scaled_zeros, n, k).astype(np.float64))
+    return exact.astype(np.float16)
+
+
+def dequant_w8_cuda(qweight, scales_to8, scaled_zeros_to8):
+    """``(int8_t)`` (truncation toward zero) of the single-rounded fp16 value
+    (dequant_awq_format/dequant_i4_to_i8.cu:14-35,143-146)."""
+    return np.trunc(dequant_w16_cuda(qweight, scales_to8, scaled_zeros_to8).astype(np.float32)).astype(np.int8)
+
+
+def act_quant_cuda(x_f16):
+    """Activation quantization as quant_kernel computes it (quant/quant_f16_to_i8.cu:54-77):
+    ``sx = fp16(amax / 127)``, ``q = sat_s8(rint(x * (127 / amax)))``, no clamp of amax.
+
+    The kernel is built with --use_fast_math, so both divisions are the GPU's approximate division, whose
+    last bit no CPU restatement can promise.  This function divides exactly (IEEE) and also returns a mask
+    of the elements that sit close enough to a rounding boundary for a 2-ulp error of ``127 / amax`` to move
+    them, and of the tokens whose scale lies next to an fp16 rounding boundary; everywhere else the result is
+    the kernel's.  The bit-level pin of those is the comparison with the reference's own extension on the GPU
+    and the committed fixtures it produced.  Returns (q int8 [M,K], sx fp16 [M], unsure_q bool [M,K],
+    unsure_sx bool [M])."""
+    x32 = np.asarray(x_f16).astype(np.float32)
+    amax = np.abs(x32).max(axis=1, keepdims=True)
+    with np.errstate(divide='ignore', invalid='ignore'):
+        mult = (np.float32(127) / amax).astype(np.float32)
+        prod = (x32 * mult).astype(np.float32)
+        sc = (amax / np.float32(127)).astype(np.float32)
+    q = np.clip(np.rint(np.nan_to_num(prod, nan=0.0, posinf=127.0, neginf=-128.0)), -128, 127).astype(np.int8)
+    frac = np.abs(prod - np.floor(prod) - np.float32(0.5))
+    unsure_q = ~(frac > np.abs(prod) * np.float32(4e-7) + np.float32(1e-30))
+    sx = sc.astype(np.float16).reshape(-1)
+    lo = (sc * np.float32(1 - 3e-7)).astype(np.float16).reshape(-1)
+    hi = (sc * np.float32(1 + 3e-7)).astype(np.float16).reshape(-1)
+    return q, sx, unsure_q, (lo != hi)
+
+
+def y_w8a8_cuda(xq, sx, w8, scales_1):
+    """The W8A8 GEMM alone on given int8 operands: ``half(float(acc) * (float(s1[n]) * float(sx[m])))``
+    (thirdparty/AWQ/kernels/csrc/w8a8/w8a8_gemm_cuda.cu:896-901)."""
+    sc = scales_1.astype(np.float32)[None, :] * sx.astype(np.float32)[:, None]
+    return (acc_int32(xq, w8).astype(np.float32) * sc).astype(np.float16)
 
 
 # --------------------------------------------------------------------------
