@@ -966,23 +966,76 @@ struct Plan {
     size_t partial_bytes;
 };
 
-// Split-K plan.  When a problem has fewer output tiles than the device has SMs, a tile's K range is cut
-// into runs of whole stage bundles, one CTA each, and a second pass sums the partial tiles.  Measured on
-// B200: with a tile for three SMs in four or more, the second pass and the partial traffic cost more than the
-// idle SMs, so only problems with fewer tiles than SMs are split.  The partial tiles
-// (tiles * splits * BT * 128 * 4 bytes) must fit `max_partial_bytes` (the caller's scratch, if bounded).
+// Split-K plan, old rule (dequantizing modes, token tiles up to 64, the tensor-memory W4A16 kernel).  When a
+// problem has fewer output tiles than the device has SMs, a tile's K range is cut into runs of whole stage
+// bundles, one CTA each, and a second pass sums the partial tiles.  Measured on B200: with a tile for three
+// SMs in four or more, the second pass and the partial traffic cost more than the idle SMs, so only problems
+// with fewer tiles than SMs are split.  The partial tiles (tiles * splits * BT * 128 * 4 bytes) must fit
+// `max_partial_bytes` (the caller's scratch, if bounded).
 // `w4_tmem` selects the geometry of the W4A16 kernel that keeps the expanded operand in tensor memory:
 // token tiles of 32..128 and stages of one quantization group.
-static Plan make_plan(int M, int N, int K, bool int8, size_t max_partial_bytes = ~(size_t)0, bool w4_tmem = false) {
+static Plan plan_geometry(int M, int N, int K, bool int8, int bt, int sub) {
     Plan pl;
-    pl.bt = token_tile(M);
-    if (w4_tmem) pl.bt = pl.bt < 32 ? 32 : (pl.bt > 128 ? 128 : pl.bt);
+    pl.bt = bt;
     pl.n_tiles = (N + kTileN - 1) / kTileN;
-    pl.m_tiles = (M + pl.bt - 1) / pl.bt;
-    const int sub = w4_tmem ? 2 : stage_bundle(pl.bt);
+    pl.m_tiles = (M + bt - 1) / bt;
     const int stages_total = (K / (int8 ? 128 : 64) + sub - 1) / sub;   // k blocks past K are zero-filled
     pl.kb_total = stages_total * sub;
     pl.kb_per_split = sub;                                              // bundle size (see unit_range)
+    pl.splits = 1;
+    pl.partial_bytes = 0;
+    return pl;
+}
+
+// Plan of the TMA-fed modes (W8A8, FP16) beyond 64 tokens: token tile and K split chosen together by a cost
+// model fitted to graph-timed runs on B200 (K = 4096 and 14336, N = 1024..14336, M = 128..2048):
+//   * a CTA needs c(BT) microseconds per 128-byte k block (0.34 / 0.375 / 0.53 for int8 at BT = 64 / 128 / 256:
+//     the 16 KB weight block, not the MMA, sets the pace of small token tiles), so one round of tiles takes
+//     kb * c and smaller token tiles pay when they fill SMs that larger ones leave idle;
+//   * all CTAs together draw their operands from L2 at about 11.5 TB/s, which bounds many small tiles;
+//   * a K split costs about 6 us (second launch, drained pipeline) plus its partial-tile traffic, so it pays
+//     only for very few tiles or long K (it made M = 256..512 on 4096 x 4096 1.5x SLOWER than unsplit tiles).
+static Plan make_plan_tma(int M, int N, int K, bool int8, size_t max_partial_bytes) {
+    const int sms = device_sm_count();
+    const double es = int8 ? 1.0 : 2.0;
+    Plan best;
+    double best_cost = 1e30;
+    for (int bt = 256; bt >= 64; bt >>= 1) {
+        if (bt > token_tile(M)) continue;
+        const int sub = stage_bundle(bt);
+        Plan pl = plan_geometry(M, N, K, int8, bt, sub);
+        const int tiles = pl.n_tiles * pl.m_tiles, stages_total = pl.kb_total / sub;
+        const double c = (bt == 64 ? 0.34 : bt == 128 ? 0.375 : 0.53) * (int8 ? 1.0 : 0.77);
+        const double t_bw = (double)tiles * (kTileN + bt) * K * es / 11.5e6;
+        const size_t tile_bytes = (size_t)bt * kTileN * 4;
+        const int min_stages = 4 / sub > 0 ? 4 / sub : 1;                 // at least 4 k blocks per run
+        int max_s = tiles < sms ? sms / tiles : 1;
+        if (max_s > stages_total / min_stages) max_s = stages_total / min_stages > 0 ? stages_total / min_stages : 1;
+        for (int sp = 1; sp <= max_s; ++sp) {
+            if (sp > 1 && (size_t)tiles * sp * tile_bytes > max_partial_bytes) break;
+            const int rounds = (tiles * sp + sms - 1) / sms;
+            const double t_lat = rounds * ((double)pl.kb_total / sp) * c;
+            double cost = t_lat > t_bw ? t_lat : t_bw;
+            if (sp > 1) cost += 6.0 + (double)tiles * sp * tile_bytes / 2.0e6;
+            if (cost < best_cost - 1e-9) {
+                best_cost = cost;
+                best = pl;
+                best.splits = sp;
+                best.partial_bytes = sp > 1 ? (size_t)tiles * sp * tile_bytes : 0;
+            }
+        }
+    }
+    return best;
+}
+
+static Plan make_plan(int M, int N, int K, bool int8, size_t max_partial_bytes = ~(size_t)0, bool w4_tmem = false,
+                      bool tma_fed = false) {
+    if (tma_fed && M > 64) return make_plan_tma(M, N, K, int8, max_partial_bytes);
+    int bt = token_tile(M);
+    if (w4_tmem) bt = bt < 32 ? 32 : (bt > 128 ? 128 : bt);
+    const int sub = w4_tmem ? 2 : stage_bundle(bt);
+    Plan pl = plan_geometry(M, N, K, int8, bt, sub);
+    const int stages_total = pl.kb_total / sub;
     const int tiles = pl.n_tiles * pl.m_tiles;
     const int sms = device_sm_count();
     const size_t tile_bytes = (size_t)pl.bt * kTileN * 4;
@@ -1002,10 +1055,11 @@ static Plan make_plan(int M, int N, int K, bool int8, size_t max_partial_bytes =
 
 size_t gemm_workspace_bytes(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    const Plan a = make_plan(M, N, K, false), b = make_plan(M, N, K, true),
-               c = make_plan(M, N, K, false, ~(size_t)0, M <= 128);
+    const Plan a = make_plan(M, N, K, false, ~(size_t)0, false, true), b = make_plan(M, N, K, true, ~(size_t)0, false, true),
+               c = make_plan(M, N, K, false, ~(size_t)0, M <= 128), d = make_plan(M, N, K, false);
     size_t need = a.partial_bytes > b.partial_bytes ? a.partial_bytes : b.partial_bytes;
-    return need > c.partial_bytes ? need : c.partial_bytes;
+    if (c.partial_bytes > need) need = c.partial_bytes;
+    return need > d.partial_bytes ? need : d.partial_bytes;
 }
 
 struct GemmArgs {
@@ -1154,7 +1208,7 @@ int launch_gemm(const GemmArgs& a) {
     // W4A16: up to 128 tokens the kernel that keeps the expanded operand in tensor memory (its token tiles stop
     // at 128); beyond, the shared-memory expander kernel with 256-token tiles
     const bool w4_tmem = kMode == kModeW4 && a.M <= 128;
-    const Plan pl = make_plan(a.M, a.N, a.K, kInt8, a.plan_cap ? a.plan_cap : ~(size_t)0, w4_tmem);
+    const Plan pl = make_plan(a.M, a.N, a.K, kInt8, a.plan_cap ? a.plan_cap : ~(size_t)0, w4_tmem, kMode == kModeTma);
     if (pl.partial_bytes > 0 && (!a.workspace || ((uintptr_t)a.workspace & 15) || a.workspace_bytes < pl.partial_bytes))
         return KAIROS_ERR_WORKSPACE;
     if constexpr (kMode == kModeW4) {

@@ -162,7 +162,7 @@ class DynamicLinear(torch.nn.Module):
             x = x.contiguous()
         m = x.shape[0]
         if out is None:
-            out = torch.empty((m, self.out_features), dtype=torch.float16, device=x.device)
+            out = x.new_empty((m, self.out_features))      # the cheapest allocation call torch offers from Python
         elif out.shape != (m, self.out_features) or out.dtype != torch.float16 or not out.is_contiguous():
             raise ValueError('out must be a contiguous fp16 [M, N] tensor')
         rc = _switched_linear(self._handle or self._native(), x.data_ptr(), out.data_ptr(), m, comp_type,

@@ -226,12 +226,14 @@ def test_gemv_bias_and_fixture(kb):
 # ------------------------------------------------------------------ a11 W8A8
 GEMM_SHAPES = [(1, 128, 256), (5, 256, 64), (16, 512, 128), (33, 1152, 96), (16, 4096, 4096), (64, 4096, 1024),
                (100, 4096, 4096), (128, 14336, 4096), (257, 3584, 512), (512, 4096, 4096), (1000, 4096, 1024),
-               # CTA-pair kernel (M >= 512 and >= 74 tile pairs), ragged in M and N
-               (777, 1024, 9480)]
+               # ragged in M and N, several token tiles; token tiles of 128 and 64 chosen by the plan's cost model
+               (777, 1024, 9480), (300, 512, 2000), (600, 640, 2000),
+               # CTA-pair kernel (about five rounds of 256 x 256 tiles or more), ragged in M and N
+               (2600, 512, 9480)]
 
 
-# (1280, 512, 4100): CTA-pair kernel with N % 8 != 0, which takes its scalar stores
-@pytest.mark.parametrize('m,k,n', GEMM_SHAPES + [(1280, 512, 4100)])
+# N % 8 != 0 takes the scalar stores: (1280, 512, 4100) in the one-CTA kernel, (6000, 256, 4100) in the CTA-pair kernel
+@pytest.mark.parametrize('m,k,n', GEMM_SHAPES + [(1280, 512, 4100), (6000, 256, 4100)])
 def test_w8a8_gemm_bit_exact(kb, m, k, n):
     _, ops, _ = kb
     x, _, res = case(m, k, n, seed=m)
@@ -249,7 +251,9 @@ def test_w8a8_gemm_bit_exact(kb, m, k, n):
 
 # The code path a production call takes: no accumulator dump, so the CTA-pair kernel runs its 16-byte-store
 # epilogue (shuffled activation scales, packed fp16 conversion) and the one-CTA kernel its check-free loop.
-@pytest.mark.parametrize('m,k,n', [(777, 1024, 9480), (1280, 512, 4100), (1024, 4096, 4096), (300, 512, 1024)])
+@pytest.mark.parametrize('m,k,n', [(777, 1024, 9480), (1280, 512, 4100), (1024, 4096, 4096), (300, 512, 1024),
+                                   (512, 4096, 4096), (1000, 4096, 1024), (300, 512, 2000), (600, 640, 2004),
+                                   (2600, 512, 9480), (6000, 256, 4100)])
 def test_w8a8_gemm_production_epilogue_bit_exact(kb, m, k, n):
     _, ops, _ = kb
     x, _, res = case(m, k, n, seed=m)
