@@ -212,6 +212,23 @@ int kairos_lut_get(kairos_lut* t, int m);                   /* lut.h:22-33; KAIR
 void kairos_lut_shrink_to_fit(kairos_lut* t);               /* lut.h:40-43 */
 int kairos_lut_size(const kairos_lut* t);
 
+/* ---- tensor parallelism: all-reduce of small row-parallel outputs over peer memory ----------
+ * No counterpart in the reference (single GPU, kairos/main.py:19-23).  Sums, over the `world` ranks of a
+ * tensor-parallel group, fp16 vectors of n elements (n % 8 == 0) that each rank holds in memory its peers
+ * can address (an NVLink peer mapping made by the host, e.g. CUDA IPC or virtual-memory handles):
+ * out[i] = fp16(sum over r = 0..world-1, in rank order, of float(peer_in[r][i])), identical on every rank.
+ * peer_in[r] / peer_signal[r] are HOST arrays of `world` device pointers: rank r's partial and rank r's
+ * signal pad as mapped in THIS process.  A signal pad is kairos_peer_allreduce_signal_bytes() bytes, zeroed
+ * once before first use (on every rank, before any rank's first call).  Every rank must issue the same
+ * sequence of calls, one process per GPU, and consecutive calls must alternate between two partial buffers
+ * (a call's barrier proves the peers have finished reading the buffer of the call before the previous one).
+ * Meant for up to ~1 MB; every rank reads every partial.  The wait for the peers is bounded (about a
+ * second): on a timeout the kernel raises the device status word (kairos_device_status) and returns without
+ * writing `out`.  Plain peer loads and stores only: no multicast, no TMA, no library kernel on peer memory. */
+int kairos_peer_allreduce_signal_bytes(void);
+int kairos_peer_allreduce_f16(const void* const* peer_in, void* const* peer_signal, int world, int rank, void* out,
+                              long long n, kairos_stream_t stream);
+
 /* ---- context: bounded conversion cache + workspaces (one per device) -------------
  * The reference converts the whole weight on every call into a fresh torch.empty
  * (kairos/dynamic_linear.py:145-147,159-161); the context keeps converted weights in

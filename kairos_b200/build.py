@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 OBJ = os.path.join(HERE, 'build')
 LIB = os.path.join(HERE, 'libkairos_b200.so')
-SOURCES = ['api.cu', 'tensormap.cu', 'act_quant.cu', 'convert.cu', 'gemv.cu', 'decode_split.cu', 'gemm_sm100.cu', 'gemm2_sm100.cu', 'glue.cu', 'selftest.cu']
+SOURCES = ['api.cu', 'tensormap.cu', 'act_quant.cu', 'convert.cu', 'gemv.cu', 'decode_split.cu', 'gemm_sm100.cu', 'gemm2_sm100.cu', 'glue.cu', 'selftest.cu', 'allreduce.cu']
 NVCC_FLAGS = [
     '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
     '-fmad=false',            # bit-exact stages must not contract a*b+c; hot loops use explicit fma intrinsics

@@ -144,13 +144,15 @@ class DynamicLinear(torch.nn.Module):
     # ---- forward ----------------------------------------------------------
     # forward / _forward / forward_q8 pass raw pointers to the library and build no autograd graph; they carry
     # no torch.no_grad() wrapper because entering one costs about as much host time as the launch itself
-    def forward(self, input: torch.Tensor) -> torch.Tensor:
+    def forward(self, input: torch.Tensor, out=None) -> torch.Tensor:
+        """`out`, when given, is a contiguous fp16 [tokens, N] tensor the result is written into (for example a
+        buffer that peers of a tensor-parallel group can read); the return value is a view of it."""
         shape = input.shape
         m = input.numel() // shape[-1]
         if m != self.pre_m:
             self.pre_m = m
             self.comp_type = type(self).prof.get_comp_type(self.shape, m)
-        return self._forward(input, m, self.comp_type).view(shape[0], shape[1], -1)
+        return self._forward(input, m, self.comp_type, out).view(shape[0], shape[1], -1)
 
     def _forward(self, input: torch.Tensor, batch_token_len, comp_type, out=None) -> torch.Tensor:
         """Run kernel `comp_type` on input [M, K] (or [..., K]) and return [M, N] (written into `out`, a
@@ -180,10 +182,16 @@ class DynamicLinear(torch.nn.Module):
             self.comp_type = type(self).prof.get_comp_type(self.shape, m)
         return self.comp_type == COMP_TYPE_NAME['w8a8']
 
-    def forward_q8(self, xq, sx):
-        """W8A8 on activations that are already quantized: xq int8 [..., K], sx fp16 [tokens] -> [..., N]."""
+    def forward_q8(self, xq, sx, out=None):
+        """W8A8 on activations that are already quantized: xq int8 [..., K], sx fp16 [tokens] -> [..., N]
+        (written into `out`, a contiguous fp16 tensor of that many elements, when given)."""
         m = xq.numel() // self.in_features
-        out = torch.empty(xq.shape[:-1] + (self.out_features,), dtype=torch.float16, device=xq.device)
+        if out is None:
+            out = torch.empty(xq.shape[:-1] + (self.out_features,), dtype=torch.float16, device=xq.device)
+        elif out.numel() != m * self.out_features or out.dtype != torch.float16 or not out.is_contiguous():
+            raise ValueError('out must be a contiguous fp16 tensor of tokens x N elements')
+        else:
+            out = out.view(xq.shape[:-1] + (self.out_features,))
         rc = lib.kairos_switched_linear_q8(self._handle or self._native(), xq.data_ptr(), sx.data_ptr(), out.data_ptr(),
                                            m, _raw_stream(xq.device.index))
         if rc:

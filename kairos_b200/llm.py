@@ -10,6 +10,8 @@ captured into a CUDA graph, so the per-token host cost is one graph launch.
 """
 from __future__ import annotations
 
+import os
+
 import math
 import time
 from dataclasses import dataclass
@@ -145,7 +147,7 @@ class Decoder(torch.nn.Module):
     them as stock torch ops (what a HuggingFace model does)."""
 
     def __init__(self, cfg: DecoderConfig, device='cuda', seed=0, quant_strategy='DynamicLinear', layers=None,
-                 fuse_linears=True, glue='cuda', tp_rank=0, tp_world=1, tp_group=None):
+                 fuse_linears=True, glue='cuda', tp_rank=0, tp_world=1, tp_group=None, peer_allreduce_tokens=64):
         super().__init__()
         # Tensor parallelism (new; the reference is single-GPU): every rank builds the decoder of the SHARDED
         # geometry -- its own heads and inner channels, quantized locally, with its own LUT -- and the outputs
@@ -187,6 +189,12 @@ class Decoder(torch.nn.Module):
         self.kv = None
         self.graph = None
         self._prefill_graphs = {}
+        # Row-parallel outputs of up to `peer_allreduce_tokens` tokens are summed by the library's own kernel
+        # over NVLink peer memory (latency-bound sizes: decode steps); larger ones by NCCL.  0 = NCCL always.
+        self.peer_ar = None
+        if tp_world > 1 and peer_allreduce_tokens > 0 and os.environ.get('KAIROS_PEER_ALLREDUCE', '1') != '0':
+            from .tp import PeerAllReduce
+            self.peer_ar = PeerAllReduce(tp_group, self.device, peer_allreduce_tokens * cfg.hidden)
 
     def linear_shapes(self):
         """Distinct (N, K) of this model's switched linears (the LUT's key set)."""
@@ -245,6 +253,25 @@ class Decoder(torch.nn.Module):
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.tp_group)
         return y
 
+    def _row_parallel(self, lin, x, q8=None):
+        """A row-parallel linear (o_proj, down_proj) and the sum of its partial outputs over the group.  Small
+        outputs are written straight into the peer-addressable buffer and summed by the library's peer-memory
+        kernel; `q8` = (int8 activations, scales) when the operator before already quantized them."""
+        lead = (q8[0] if q8 is not None else x).shape[:-1]
+        m, n = 1, lin.out_features
+        for d in lead:
+            m *= d
+        ar = self.peer_ar
+        if ar is not None and ar.fits(m * n):
+            part = ar.partial(m, n)
+            if q8 is not None:
+                lin.forward_q8(q8[0], q8[1], out=part)
+            else:
+                lin(x if x.dim() == 3 else x.reshape(1, m, -1), out=part)
+            return ar.reduce(m, n).view(*lead, n)
+        y = lin.forward_q8(*q8) if q8 is not None else lin(x)
+        return self._reduce(y)
+
     def _norm_then_linear(self, mod, x, delta, lin):
         """lin(norm(x + delta)); when the LUT sends this M to W8A8 the norm emits the int8 activations that
         kernel consumes, with no fp16 round trip."""
@@ -294,17 +321,17 @@ class Decoder(torch.nn.Module):
             o = F.scaled_dot_product_attention(q, kc[:, :, pos0:pos0 + s], vc[:, :, pos0:pos0 + s], is_causal=True,
                                                enable_gqa=True)
         o = o.transpose(1, 2).reshape(b, s, nh * d)
-        attn_out = self._reduce(a.o_proj(o))
+        attn_out = self._row_parallel(a.o_proj, o)
         m = layer.mlp
         if not self.fuse:
             h = self._norm(layer.post_attention_layernorm, x, attn_out)
-            return self._reduce(m.down_proj(F.silu(m.gate_proj(h)) * m.up_proj(h)))
+            return self._row_parallel(m.down_proj, F.silu(m.gate_proj(h)) * m.up_proj(h))
         gu = self._norm_then_linear(layer.post_attention_layernorm, x, attn_out, m.gate_up_proj)
         if self.glue == 'cuda' and self.fuse_quant and m.down_proj.wants_int8(b * s):
             aq, sa, _ = ops.silu_mul_quant(gu)
-            return self._reduce(m.down_proj.forward_q8(aq, sa))
+            return self._row_parallel(m.down_proj, None, (aq, sa))
         act = ops.silu_mul(gu) if self.glue == 'cuda' else F.silu(gu[..., :cfg.inter]) * gu[..., cfg.inter:]
-        return self._reduce(m.down_proj(act))
+        return self._row_parallel(m.down_proj, act)
 
     def _stack(self, x, decode):
         """All layers, then the final norm (which carries the last residual addition)."""

@@ -119,6 +119,64 @@ class StepGuard:
         return errs
 
 
+class PeerAllReduce:
+    """All-reduce of small row-parallel outputs by this library's own kernel over NVLink peer memory
+    (``kairos_peer_allreduce_f16``: one flag exchange, then every rank sums all partials with plain peer
+    loads), for the sizes where a library all-reduce is pure latency (decode steps).
+
+    The partial outputs must live in memory the peers can address: two slots of ``max_elems`` fp16 values
+    allocated through ``torch.distributed._symmetric_memory`` (CUDA virtual-memory handles exchanged over the
+    group's store; multicast binding is switched off, the kernel uses plain loads).  ``partial(m, n)`` is the
+    view a row-parallel linear writes into (``DynamicLinear._forward(..., out=...)``), ``reduce(m, n)`` sums it
+    over the group into a fresh local tensor and flips the slot.  Consecutive calls alternate the slots, so a
+    CUDA graph that captures calls must hold an even number of them.  Larger messages go to NCCL.
+    """
+
+    def __init__(self, group, device, max_elems):
+        import ctypes
+        import os
+        os.environ.setdefault('TORCH_SYMM_MEM_DISABLE_MULTICAST', '1')
+        import torch.distributed._symmetric_memory as symm_mem
+        from ._lib import check, lib
+        self._lib, self._check = lib, check
+        self.group = group if group is not None else dist.distributed_c10d._get_default_group()
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.device = torch.device(device)
+        self.max_elems = (int(max_elems) + 127) // 128 * 128
+        sig = lib.kairos_peer_allreduce_signal_bytes()
+        slot_bytes = self.max_elems * 2
+        self.buf = symm_mem.empty(2 * slot_bytes + sig, dtype=torch.uint8, device=self.device)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        self.handle = symm_mem.rendezvous(self.buf, self.group.group_name)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        dist.barrier(self.group)                      # every pad is zero before any rank signals
+        arr = ctypes.c_void_p * self.world
+        self._in = [arr(*[p + s * slot_bytes for p in ptrs]) for s in (0, 1)]
+        self._sig = arr(*[p + 2 * slot_bytes for p in ptrs])
+        self._slots = [self.buf[s * slot_bytes:(s + 1) * slot_bytes].view(torch.float16) for s in (0, 1)]
+        self.turn = 0
+        self.calls = 0
+
+    def fits(self, n_elems):
+        return n_elems <= self.max_elems and n_elems % 8 == 0
+
+    def partial(self, m, n):
+        """The [m, n] fp16 view of the slot the next `reduce` will sum."""
+        return self._slots[self.turn][:m * n].view(m, n)
+
+    def reduce(self, m, n, out=None):
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.float16, device=self.device)
+        self._check(self._lib.kairos_peer_allreduce_f16(self._in[self.turn], self._sig, self.world, self.rank,
+                                                        out.data_ptr(), m * n,
+                                                        torch.cuda.current_stream(self.device).cuda_stream),
+                    'kairos_peer_allreduce_f16')
+        self.turn ^= 1
+        self.calls += 1
+        return out
+
+
 class ColumnParallelLinear(torch.nn.Module):
     def __init__(self, linear, rank, world, group=None, gather_output=False):
         super().__init__()

@@ -119,3 +119,73 @@ def test_two_gpu_tensor_parallel_decoder_graph_matches_eager():
     assert out['ranks_agree']
     assert np.array_equal(out['eager'], out['graphed'])
     assert out['status'] == 0
+
+
+def _peer_allreduce_worker(rank, world, port, out):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    os.environ['NCCL_NVLS_ENABLE'] = '0'
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    dist.all_reduce(torch.zeros(1, device=dev))
+    import kairos_b200 as kb
+    from kairos_b200 import tp
+    ar = tp.PeerAllReduce(None, dev, 64 * 1024)
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    ok = True
+
+    def expected(part):
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part.contiguous())
+        acc = torch.zeros(part.shape, dtype=torch.float32, device=dev)
+        for p in parts:                       # rank order, fp32, one rounding at the end
+            acc += p.float()
+        return acc.half()
+
+    for (m, n) in [(1, 8), (1, 4096), (24, 512), (3, 1000), (64, 1024)] * 2:    # eager, slots alternate
+        part = ar.partial(m, n)
+        part.copy_(torch.randn((m, n), generator=gen, device=dev, dtype=torch.float32).half())
+        want = expected(part)
+        got = ar.reduce(m, n)
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(got, want)
+    # four calls captured in one graph and replayed: sequence numbers advance on the device
+    m, n = 8, 2048
+    srcs = [torch.randn((m, n), generator=gen, device=dev, dtype=torch.float32).half() for _ in range(4)]
+    wants = [expected(s) for s in srcs]
+    outs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(4)]
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for s, o in zip(srcs, outs):
+                ar.partial(m, n).copy_(s)
+                ar.reduce(m, n, out=o)
+    for _ in range(3):
+        for o in outs:
+            o.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        ok = ok and all(torch.equal(o, w) for o, w in zip(outs, wants))
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        out['ok'] = bool(flag.item())
+        out['status'] = kb.runtime.device_status()
+    del graph
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_two_gpu_peer_memory_allreduce_is_the_rank_ordered_sum():
+    """The library's all-reduce over peer memory: bit-identical to the fp32 sum of the partials in rank order
+    on every rank, eagerly with alternating slots and replayed from a CUDA graph."""
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_peer_allreduce_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert out['ok']
+    assert out['status'] == 0
