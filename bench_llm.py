@@ -29,6 +29,8 @@ def main():
     ap.add_argument('--cache-gb', type=float, default=24.0, help='bound of the conversion cache')
     ap.add_argument('--lut', default='warm', choices=['warm', 'cold'])
     ap.add_argument('--no-fuse', action='store_true', help='keep q/k/v and gate/up as separate linears (7 per layer)')
+    ap.add_argument('--compare-allreduce', action='store_true',
+                    help='tensor parallel: measure a second time with the small all-reduces through NCCL')
     ap.add_argument('--glue', default='cuda', choices=['cuda', 'torch'], help="'torch' = stock torch ops around the linears")
     args = ap.parse_args()
 
@@ -63,11 +65,19 @@ def main():
     say(json.dumps({'model': model.cfg.name, 'tp': world, 'layers': len(model.model.layers), 'lut_seconds': round(t_lut, 1),
                       'build_seconds': round(t_build, 1), 'lut_mode': args.lut, 'lut': lut, 'fused_linears': not args.no_fuse, 'glue': args.glue,
                       'weights_gb': round(sum(b.numel() * b.element_size() for b in model.buffers()) / 2**30, 2)}))
-    for b in [int(v) for v in args.batches.split(',')]:
-        r = llm.measure_ttft_tpot(model, b, args.prompt, args.new)
-        r.update({'model': model.cfg.name, 'tp': world, 'cache': ctx.stats(),
-                  'peak_gb': round(torch.cuda.max_memory_allocated() / 2**30, 2)})
-        say(json.dumps(r), flush=True)
+    def sweep(label):
+        for b in [int(v) for v in args.batches.split(',')]:
+            r = llm.measure_ttft_tpot(model, b, args.prompt, args.new)
+            r.update({'model': model.cfg.name, 'tp': world, 'small_allreduce': label, 'cache': ctx.stats(),
+                      'peak_gb': round(torch.cuda.max_memory_allocated() / 2**30, 2)})
+            say(json.dumps(r), flush=True)
+
+    sweep('none' if world == 1 else ('peer-memory kernel' if model.peer_ar is not None else 'nccl'))
+    if world > 1 and model.peer_ar is not None and args.compare_allreduce:
+        # the same model with every all-reduce through NCCL (the decode graph is captured again)
+        model.release_graphs()
+        model.peer_ar = None
+        sweep('nccl')
     if world > 1:
         model.release_graphs()      # captured collectives must be gone before the group is destroyed
         dist.barrier()

@@ -27,7 +27,7 @@ namespace kairos {
 
 int* device_status_word();    // api.cu
 
-constexpr int kArBlocks = 32;        // blocks per launch = signal slots per peer
+constexpr int kArBlocks = 128;       // most blocks per launch = signal slots per peer (a launch uses 4..128 by size)
 constexpr int kArThreads = 256;
 constexpr int kArMaxWorld = 8;
 
@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(const ArP
         if (threadIdx.x == 0) atomicExch(p.status, KAIROS_ERR_DEVICE);
         return;
     }
-    for (long long i = (long long)b * kArThreads + threadIdx.x; i < p.words; i += (long long)kArBlocks * kArThreads) {
+    for (long long i = (long long)b * kArThreads + threadIdx.x; i < p.words; i += (long long)gridDim.x * kArThreads) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -148,7 +148,12 @@ extern "C" int kairos_peer_allreduce_f16(const void* const* peer_in, void* const
     p.rank = rank;
     p.status = device_status_word();
     if (!p.status) return KAIROS_ERR_CUDA;
-    const cudaError_t e = launch_chained(oneshot_allreduce_kernel, dim3(kArBlocks), dim3(kArThreads), 0,
+    // one 16-byte word per thread up to 128 blocks: a block's flag exchange runs beside the others', so more
+    // blocks cost no latency, while a block that loops pays a peer round trip per iteration.  Every rank passes
+    // the same n, so the ranks agree on the blocks that take part (each block keeps its own sequence).
+    long long want = (p.words + kArThreads - 1) / kArThreads;
+    const int blocks = want < 4 ? 4 : (want > kArBlocks ? kArBlocks : (int)want);
+    const cudaError_t e = launch_chained(oneshot_allreduce_kernel, dim3(blocks), dim3(kArThreads), 0,
                                          reinterpret_cast<cudaStream_t>(stream), p);
     if (e != cudaSuccess) return note_cuda_error(e);
     return launch_status();
