@@ -228,6 +228,16 @@ int kairos_lut_size(const kairos_lut* t);
 int kairos_peer_allreduce_signal_bytes(void);
 int kairos_peer_allreduce_f16(const void* const* peer_in, void* const* peer_signal, int world, int rank, void* out,
                               long long n, kairos_stream_t stream);
+/* The same sum folded into its consumer: kairos_add_rms_norm / kairos_rms_norm_quant whose pending delta is the
+ * output [M, K] of a row-parallel linear still spread over the group (M <= 128 tokens, one signal slot per
+ * token).  X += fp16(sum of the partials in rank order) in place, then the norm: the bits of
+ * kairos_peer_allreduce_f16 followed by kairos_add_rms_norm / kairos_rms_norm_quant, without the kernel and the
+ * round trip in between.  Counts as one call in the sequence every rank must issue alike. */
+int kairos_add_rms_norm_peer(void* X, const void* const* peer_in, void* const* peer_signal, int world, int rank,
+                             const void* W, void* Y, int M, int K, float eps, kairos_stream_t stream);
+int kairos_rms_norm_quant_peer(void* X, const void* const* peer_in, void* const* peer_signal, int world, int rank,
+                               const void* W, void* Y_or_null, void* Xq, void* sx, int M, int K, float eps,
+                               kairos_stream_t stream);
 
 /* ---- context: bounded conversion cache + workspaces (one per device) -------------
  * The reference converts the whole weight on every call into a fresh torch.empty

@@ -44,6 +44,10 @@ SIGNATURES = {
     'kairos_rope_kv': (c_int, [c_void_p] * 4 + [c_int] + [c_void_p] * 3 + [c_int] * 6 + [c_void_p]),
     'kairos_peer_allreduce_signal_bytes': (c_int, []),
     'kairos_peer_allreduce_f16': (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, ctypes.c_longlong, c_void_p]),
+    'kairos_add_rms_norm_peer': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                         ctypes.c_float, c_void_p]),
+    'kairos_rms_norm_quant_peer': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_int, c_int, ctypes.c_float, c_void_p]),
     'kairos_lut_create': (c_void_p, []),
     'kairos_lut_destroy': (None, [c_void_p]),
     'kairos_lut_record': (c_int, [c_void_p, c_int, c_int]),

@@ -21,100 +21,46 @@
 // device status word, skips the sum and returns, leaving the context usable.
 //
 // Only plain loads and stores touch peer memory: no TMA, no multicast, no library kernel.
-#include "common.cuh"
+#include "peer.cuh"
 
 namespace kairos {
 
 int* device_status_word();    // api.cu
 
-constexpr int kArBlocks = 128;       // most blocks per launch = signal slots per peer (a launch uses 4..128 by size)
-constexpr int kArThreads = 256;
-constexpr int kArMaxWorld = 8;
-
 struct ArParams {
-    const uint4* in[kArMaxWorld];     // every rank's partial (slot of this call), [n / 8] 16-byte words
-    uint32_t* signal[kArMaxWorld];    // every rank's signal pad: [world][kArBlocks] sequence numbers
-    uint32_t* counter;                // this rank's [kArBlocks] sequence counters
+    PeerSet peers;                    // every rank's partial (slot of this call) and signal pad
     uint4* out;                       // local output
     long long words;                  // n / 8
-    int world, rank;
-    int* status;
 };
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint4 ld_peer(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p)
-                 : "memory");
-    return v;
-}
 
 __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(const ArParams p) {
     chain_release();
     chain_wait();                      // the partial was written by the kernel before this one in the stream
-    __shared__ uint32_t s_seq;
-    __shared__ int s_ok;
-    const int b = blockIdx.x;
-    if (threadIdx.x == 0) {
-        s_seq = p.counter[b] + 1;
-        s_ok = 1;
+    if (!peer_barrier(p.peers, blockIdx.x)) return;
+    for (long long i = (long long)blockIdx.x * kArThreads + threadIdx.x; i < p.words;
+         i += (long long)gridDim.x * kArThreads)
+        p.out[i] = peer_sum8(p.peers, i);
+}
+
+int make_peer_set(PeerSet* ps, const void* const* peer_in, void* const* peer_signal, int world, int rank) {
+    if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world) return KAIROS_ERR_SHAPE;
+    if (!peer_in || !peer_signal) return KAIROS_ERR_ALIGN;
+    for (int r = 0; r < kArMaxWorld; ++r) {
+        ps->in[r] = nullptr;
+        ps->signal[r] = nullptr;
     }
-    __syncthreads();
-    const uint32_t seq = s_seq;
-    if (threadIdx.x < p.world) {
-        const int peer = threadIdx.x;
-        // the stores of the producing kernel are ordered before this release by the stream order and the fence
-        __threadfence_system();
-        st_release_sys(p.signal[peer] + p.rank * kArBlocks + b, seq);
-        const uint32_t* mine = p.signal[p.rank] + peer * kArBlocks + b;
-        bool ok = false;
-        for (int spin = 0; spin < (1 << 21); ++spin) {          // ~1 s with the sleeps below
-            if ((int32_t)(ld_acquire_sys(mine) - seq) >= 0) { ok = true; break; }
-            if (spin > 64) __nanosleep(spin > 4096 ? 500 : 40);
-        }
-        if (!ok) s_ok = 0;
+    for (int r = 0; r < world; ++r) {
+        if (!peer_in[r] || !peer_signal[r] || ((uintptr_t)peer_in[r] & 15) || ((uintptr_t)peer_signal[r] & 3))
+            return KAIROS_ERR_ALIGN;
+        ps->in[r] = static_cast<const uint4*>(peer_in[r]);
+        ps->signal[r] = static_cast<uint32_t*>(peer_signal[r]);
     }
-    __syncthreads();
-    if (threadIdx.x == 0) p.counter[b] = seq;                  // stay in step with the peers even after a timeout
-    if (!s_ok) {
-        if (threadIdx.x == 0) atomicExch(p.status, KAIROS_ERR_DEVICE);
-        return;
-    }
-    for (long long i = (long long)b * kArThreads + threadIdx.x; i < p.words; i += (long long)gridDim.x * kArThreads) {
-        float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        uint4 v[kArMaxWorld];
-#pragma unroll
-        for (int r = 0; r < kArMaxWorld; ++r)
-            if (r < p.world) v[r] = ld_peer(p.in[r] + i);       // all loads in flight before the first add
-#pragma unroll
-        for (int r = 0; r < kArMaxWorld; ++r) {
-            if (r < p.world) {
-                const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 f = __half22float2(h[j]);
-                    acc[2 * j] += f.x;
-                    acc[2 * j + 1] += f.y;
-                }
-            }
-        }
-        uint4 o;
-        __half2* oh = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
-        p.out[i] = o;
-    }
+    // this rank's counters sit behind the [ranks][slots] sequence numbers of its own pad
+    ps->counter = ps->signal[rank] + kArMaxWorld * kArBlocks;
+    ps->world = world;
+    ps->rank = rank;
+    ps->status = device_status_word();
+    return ps->status ? KAIROS_OK : KAIROS_ERR_CUDA;
 }
 
 }  // namespace kairos
@@ -126,28 +72,14 @@ extern "C" int kairos_peer_allreduce_signal_bytes(void) {
 extern "C" int kairos_peer_allreduce_f16(const void* const* peer_in, void* const* peer_signal, int world, int rank,
                                          void* out, long long n, kairos_stream_t stream) {
     using namespace kairos;
-    if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world || n < 0 || (n % 8) != 0) return KAIROS_ERR_SHAPE;
-    if (!peer_in || !peer_signal || !out || ((uintptr_t)out & 15)) return KAIROS_ERR_ALIGN;
-    if (n == 0) return KAIROS_OK;
+    if (n < 0 || (n % 8) != 0) return KAIROS_ERR_SHAPE;
+    if (!out || ((uintptr_t)out & 15)) return KAIROS_ERR_ALIGN;
     ArParams p;
-    for (int r = 0; r < kArMaxWorld; ++r) {
-        p.in[r] = nullptr;
-        p.signal[r] = nullptr;
-    }
-    for (int r = 0; r < world; ++r) {
-        if (!peer_in[r] || !peer_signal[r] || ((uintptr_t)peer_in[r] & 15) || ((uintptr_t)peer_signal[r] & 3))
-            return KAIROS_ERR_ALIGN;
-        p.in[r] = static_cast<const uint4*>(peer_in[r]);
-        p.signal[r] = static_cast<uint32_t*>(peer_signal[r]);
-    }
-    // this rank's counters sit behind the [world][blocks] slots of its own pad
-    p.counter = p.signal[rank] + kArMaxWorld * kArBlocks;
+    const int rc = make_peer_set(&p.peers, peer_in, peer_signal, world, rank);
+    if (rc != KAIROS_OK) return rc;
+    if (n == 0) return KAIROS_OK;
     p.out = static_cast<uint4*>(out);
     p.words = n / 8;
-    p.world = world;
-    p.rank = rank;
-    p.status = device_status_word();
-    if (!p.status) return KAIROS_ERR_CUDA;
     // one 16-byte word per thread up to 128 blocks: a block's flag exchange runs beside the others', so more
     // blocks cost no latency, while a block that loops pays a peer round trip per iteration.  Every rank passes
     // the same n, so the ranks agree on the blocks that take part (each block keeps its own sequence).

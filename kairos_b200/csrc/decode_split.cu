@@ -222,8 +222,17 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
         // refill the slot read in the previous iteration: every lane is done with it
         __syncwarp();
         if (it + kStages - 1 < n_it) {
-            issue_weights(fs, g_first + it + kStages - 1);
-            issue_x(fs, g_first + it + kStages - 1);
+            // both arrivals and the four copies of the stage from one elected lane
+            if (elect_one()) {
+                const int grp = g_first + it + kStages - 1;
+                uint8_t* st = ring + fs * kStageBytes;
+                mbar_arrive_expect_tx(&full[fs], Cfg::kWBytes + Cfg::kFTx);
+                mbar_arrive_expect_tx(&full[fs], Cfg::kXBytes);
+                tma_load_2d(st, &tmap_w, &full[fs], grp * 256, row0 / 4);
+                tma_load_2d(st + Cfg::kWBytes, &tmap_x, &full[fs], grp * kGroup, 0);
+                tma_load_2d(st + Cfg::kWBytes + Cfg::kXBytes, &tmap_s, &full[fs], row0, grp);
+                tma_load_2d(st + Cfg::kWBytes + Cfg::kXBytes + 128, &tmap_z, &full[fs], row0, grp);
+            }
         }
         if (!mbar_wait(&full[s], parity, abort_flag)) { ok = false; break; }
         const uint32_t so = (uint32_t)(s * kStageBytes);
@@ -270,11 +279,13 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
             const uint4 raw0 = lds16(w_lane + so + 1024 * rb);         // row g of the block
             const uint4 raw1 = lds16(w_lane + so + 1024 * rb + 512);   // row g + 8
             const uint32_t w0[4] = {raw0.x, raw0.y, raw0.z, raw0.w}, w1[4] = {raw1.x, raw1.y, raw1.z, raw1.w};
-            float cacc[NT][4];
+            // two accumulators per token tile (nibbles b = 0, 1 and b = 2, 3): chains of four dependent MMAs
+            // instead of eight
+            float cacc[NT][4], cacc2[NT][4];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) cacc[nt][i] = 0.f;
+                for (int i = 0; i < 4; ++i) cacc[nt][i] = cacc2[nt][i] = 0.f;
 #pragma unroll
             for (int cp = 0; cp < 4; cp += 2) {
                 // words cp, cp + 1: nibble b of each half = k 8 b + 2 c (+1); e[b] = half2(1024 + q) (b even) or
@@ -289,7 +300,8 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                     for (int b = 0; b < 4; ++b)
-                        mma16816(cacc[nt], e00[b], e10[b], e01[b], e11[b], xw[nt][4 * b + cp], xw[nt][4 * b + cp + 1]);
+                        mma16816(b < 2 ? cacc[nt] : cacc2[nt], e00[b], e10[b], e01[b], e11[b], xw[nt][4 * b + cp],
+                                 xw[nt][4 * b + cp + 1]);
             }
             float sc[2], zc[2];
 #pragma unroll
@@ -302,7 +314,7 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float qx = cacc[nt][i] - x_off[nt][i & 1];
+                    const float qx = (cacc[nt][i] + cacc2[nt][i]) - x_off[nt][i & 1];
                     acc[rb][nt][i] = fmaf(sc[i >> 1], qx, acc[rb][nt][i]);
                     acc[rb][nt][i] = fmaf(zc[i >> 1], x_sum[nt][i & 1], acc[rb][nt][i]);
                 }

@@ -5,6 +5,7 @@
 // decoder these steps are ~40 small kernels per layer and dominate both the decode step and the
 // non-GEMM part of prefill.  All are HBM-bound: 2 bytes read + 2 bytes written per element.
 #include "common.cuh"
+#include "peer.cuh"
 
 namespace kairos {
 
@@ -24,14 +25,33 @@ __device__ __forceinline__ uint4 load_residual(__half* X, const __half* H, size_
     return v;
 }
 
+// The same with the pending delta still spread over a tensor-parallel group: the delta is the output of a
+// row-parallel linear, every rank holds its partial in peer-addressable memory, and the norm sums the partials in
+// rank order (fp32, one rounding to fp16: the bits the stand-alone all-reduce produces) while it loads them.
+// The all-reduce then costs no kernel of its own.
+__device__ __forceinline__ uint4 load_residual_peer(__half* X, const PeerSet& ps, size_t row_off, int c) {
+    uint4* xp = reinterpret_cast<uint4*>(X + row_off) + c;
+    uint4 v = __ldcg(xp);
+    const uint4 h4 = peer_sum8(ps, (long long)(row_off >> 3) + c);
+    __half2* a = reinterpret_cast<__half2*>(&v);
+    const __half2* b = reinterpret_cast<const __half2*>(&h4);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = __hadd2(a[i], b[i]);
+    *xp = v;
+    return v;
+}
+
 // y = half( float(x) * rsqrt(mean(x^2) + eps) * float(w) ), one CTA per token, row kept in registers
-template <int R>
-__global__ void __launch_bounds__(256) rms_norm_kernel(__half* X, const __half* __restrict__ H,
+template <int R, bool kPeer>
+__global__ void __launch_bounds__(256) rms_norm_kernel(__half* X, const __half* __restrict__ H, const PeerSet ps,
                                                        const __half* __restrict__ W, __half* __restrict__ Y, int K,
                                                        float eps) {
     chain_release();
     chain_wait();
     const int token = blockIdx.x;
+    if constexpr (kPeer) {
+        if (!peer_barrier(ps, token)) return;       // the token's row of every rank's partial is complete
+    }
     const int chunks = K >> 3;
     uint4 v[R];
     float ss = 0.f;
@@ -39,7 +59,8 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(__half* X, const __half* 
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * 256;
         if (c < chunks) {
-            v[r] = load_residual(X, H, (size_t)token * K, c);
+            if constexpr (kPeer) v[r] = load_residual_peer(X, ps, (size_t)token * K, c);
+            else v[r] = load_residual(X, H, (size_t)token * K, c);
             const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -133,8 +154,8 @@ __device__ __forceinline__ float absmax8(const uint4& v) {
 // RMSNorm that hands its result to a W8A8 linear in the precision that kernel consumes: the fp16 result is
 // formed in registers, quantized per token to int8 (+ fp16 scale) and written ONCE as int8; the fp16 tensor
 // is written only when a consumer needs it (Y != null).  Output equals act_quant(rms_norm(X)) bit for bit.
-template <int R>
-__global__ void __launch_bounds__(256) rms_norm_quant_kernel(__half* X, const __half* __restrict__ H,
+template <int R, bool kPeer>
+__global__ void __launch_bounds__(256) rms_norm_quant_kernel(__half* X, const __half* __restrict__ H, const PeerSet ps,
                                                              const __half* __restrict__ W, __half* __restrict__ Y,
                                                              int8_t* __restrict__ Xq, __half* __restrict__ sx, int K,
                                                              float eps) {
@@ -142,6 +163,9 @@ __global__ void __launch_bounds__(256) rms_norm_quant_kernel(__half* X, const __
     chain_release();
     chain_wait();
     const int token = blockIdx.x;
+    if constexpr (kPeer) {
+        if (!peer_barrier(ps, token)) return;
+    }
     const int chunks = K >> 3;
     uint4 v[R];
     float ss = 0.f;
@@ -149,7 +173,8 @@ __global__ void __launch_bounds__(256) rms_norm_quant_kernel(__half* X, const __
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * 256;
         if (c < chunks) {
-            v[r] = load_residual(X, H, (size_t)token * K, c);
+            if constexpr (kPeer) v[r] = load_residual_peer(X, ps, (size_t)token * K, c);
+            else v[r] = load_residual(X, H, (size_t)token * K, c);
             const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -287,23 +312,30 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const __half* __restrict__
 }  // namespace kairos
 
 namespace kairos {
-static int run_rms_norm(void* X, const void* H, const void* W, void* Y, int M, int K, float eps, cudaStream_t st) {
+static int run_rms_norm(void* X, const void* H, const void* W, void* Y, int M, int K, float eps, cudaStream_t st,
+                        const PeerSet* peers = nullptr) {
     __half* x = static_cast<__half*>(X);
     const __half* h = static_cast<const __half*>(H);
     const __half* w = static_cast<const __half*>(W);
     __half* y = static_cast<__half*>(Y);
     const int per = (K / 8 + 255) / 256;
+    PeerSet ps = {};
+    if (peers) ps = *peers;
     cudaError_t e;
-    if (per <= 1) e = launch_chained(rms_norm_kernel<1>, dim3(M), dim3(256), 0, st, x, h, w, y, K, eps);
-    else if (per <= 2) e = launch_chained(rms_norm_kernel<2>, dim3(M), dim3(256), 0, st, x, h, w, y, K, eps);
-    else if (per <= 4) e = launch_chained(rms_norm_kernel<4>, dim3(M), dim3(256), 0, st, x, h, w, y, K, eps);
-    else e = launch_chained(rms_norm_kernel<8>, dim3(M), dim3(256), 0, st, x, h, w, y, K, eps);
+#define KAIROS_NORM(R)                                                                                             \
+    (peers ? launch_chained(rms_norm_kernel<R, true>, dim3(M), dim3(256), 0, st, x, h, ps, w, y, K, eps)           \
+           : launch_chained(rms_norm_kernel<R, false>, dim3(M), dim3(256), 0, st, x, h, ps, w, y, K, eps))
+    if (per <= 1) e = KAIROS_NORM(1);
+    else if (per <= 2) e = KAIROS_NORM(2);
+    else if (per <= 4) e = KAIROS_NORM(4);
+    else e = KAIROS_NORM(8);
+#undef KAIROS_NORM
     if (e != cudaSuccess) return note_cuda_error(e);
     return launch_status();
 }
 
 static int run_rms_norm_quant(void* X, const void* H, const void* W, void* Y, void* Xq, void* sx, int M, int K,
-                              float eps, cudaStream_t st) {
+                              float eps, cudaStream_t st, const PeerSet* peers = nullptr) {
     __half* x = static_cast<__half*>(X);
     const __half* h = static_cast<const __half*>(H);
     const __half* w = static_cast<const __half*>(W);
@@ -311,11 +343,17 @@ static int run_rms_norm_quant(void* X, const void* H, const void* W, void* Y, vo
     int8_t* q = static_cast<int8_t*>(Xq);
     __half* s = static_cast<__half*>(sx);
     const int per = (K / 8 + 255) / 256;
+    PeerSet ps = {};
+    if (peers) ps = *peers;
     cudaError_t e;
-    if (per <= 1) e = launch_chained(rms_norm_quant_kernel<1>, dim3(M), dim3(256), 0, st, x, h, w, y, q, s, K, eps);
-    else if (per <= 2) e = launch_chained(rms_norm_quant_kernel<2>, dim3(M), dim3(256), 0, st, x, h, w, y, q, s, K, eps);
-    else if (per <= 4) e = launch_chained(rms_norm_quant_kernel<4>, dim3(M), dim3(256), 0, st, x, h, w, y, q, s, K, eps);
-    else e = launch_chained(rms_norm_quant_kernel<8>, dim3(M), dim3(256), 0, st, x, h, w, y, q, s, K, eps);
+#define KAIROS_NORMQ(R)                                                                                                  \
+    (peers ? launch_chained(rms_norm_quant_kernel<R, true>, dim3(M), dim3(256), 0, st, x, h, ps, w, y, q, s, K, eps)     \
+           : launch_chained(rms_norm_quant_kernel<R, false>, dim3(M), dim3(256), 0, st, x, h, ps, w, y, q, s, K, eps))
+    if (per <= 1) e = KAIROS_NORMQ(1);
+    else if (per <= 2) e = KAIROS_NORMQ(2);
+    else if (per <= 4) e = KAIROS_NORMQ(4);
+    else e = KAIROS_NORMQ(8);
+#undef KAIROS_NORMQ
     if (e != cudaSuccess) return note_cuda_error(e);
     return launch_status();
 }
@@ -338,6 +376,33 @@ extern "C" int kairos_add_rms_norm(void* X, const void* H, const void* W, void* 
         ((uintptr_t)Y & 15))
         return KAIROS_ERR_ALIGN;
     return run_rms_norm(X, H, W, Y, M, K, eps, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int kairos_add_rms_norm_peer(void* X, const void* const* peer_in, void* const* peer_signal, int world, int rank,
+                                        const void* W, void* Y, int M, int K, float eps, kairos_stream_t stream) {
+    using namespace kairos;
+    if (M < 0 || M > kArBlocks || K <= 0 || (K % 8) != 0 || K > 8 * 256 * 8) return KAIROS_ERR_SHAPE;
+    if (!X || !W || !Y || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)Y & 15)) return KAIROS_ERR_ALIGN;
+    PeerSet ps;
+    const int rc = make_peer_set(&ps, peer_in, peer_signal, world, rank);
+    if (rc != KAIROS_OK) return rc;
+    if (M == 0) return KAIROS_OK;
+    return run_rms_norm(X, nullptr, W, Y, M, K, eps, reinterpret_cast<cudaStream_t>(stream), &ps);
+}
+
+extern "C" int kairos_rms_norm_quant_peer(void* X, const void* const* peer_in, void* const* peer_signal, int world,
+                                          int rank, const void* W, void* Y_or_null, void* Xq, void* sx, int M, int K,
+                                          float eps, kairos_stream_t stream) {
+    using namespace kairos;
+    if (M < 0 || M > kArBlocks || K <= 0 || (K % 16) != 0 || K > 8 * 256 * 8) return KAIROS_ERR_SHAPE;
+    if (!X || !W || !Xq || !sx || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)Xq & 15) ||
+        ((uintptr_t)Y_or_null & 15))
+        return KAIROS_ERR_ALIGN;
+    PeerSet ps;
+    const int rc = make_peer_set(&ps, peer_in, peer_signal, world, rank);
+    if (rc != KAIROS_OK) return rc;
+    if (M == 0) return KAIROS_OK;
+    return run_rms_norm_quant(X, nullptr, W, Y_or_null, Xq, sx, M, K, eps, reinterpret_cast<cudaStream_t>(stream), &ps);
 }
 
 extern "C" int kairos_silu_mul(const void* GU, void* Y, int M, int I, kairos_stream_t stream) {

@@ -192,6 +192,7 @@ class Decoder(torch.nn.Module):
         # Row-parallel outputs of up to `peer_allreduce_tokens` tokens are summed by the library's own kernel
         # over NVLink peer memory (latency-bound sizes: decode steps); larger ones by NCCL.  0 = NCCL always.
         self.peer_ar = None
+        self.fuse_peer_sum = os.environ.get('KAIROS_FUSE_PEER_SUM', '1') != '0'   # fold that sum into the next RMSNorm
         if tp_world > 1 and peer_allreduce_tokens > 0 and os.environ.get('KAIROS_PEER_ALLREDUCE', '1') != '0':
             from .tp import PeerAllReduce
             self.peer_ar = PeerAllReduce(tp_group, self.device, peer_allreduce_tokens * cfg.hidden)
@@ -243,7 +244,7 @@ class Decoder(torch.nn.Module):
         if self.glue == 'cuda':
             return ops.rms_norm(x, mod.weight, mod.eps, residual_delta=delta)
         if delta is not None:
-            x.add_(delta)
+            x.add_(self._as_tensor(delta))
         return mod(x)
 
     def _reduce(self, y):
@@ -268,9 +269,15 @@ class Decoder(torch.nn.Module):
                 lin.forward_q8(q8[0], q8[1], out=part)
             else:
                 lin(x if x.dim() == 3 else x.reshape(1, m, -1), out=part)
+            if self.glue == 'cuda' and self.fuse_peer_sum and m <= 128:
+                return ar.defer(m, n, lead)          # summed by the RMSNorm that consumes it
             return ar.reduce(m, n).view(*lead, n)
         y = lin.forward_q8(*q8) if q8 is not None else lin(x)
         return self._reduce(y)
+
+    @staticmethod
+    def _as_tensor(delta):
+        return delta.materialize() if hasattr(delta, 'materialize') else delta
 
     def _norm_then_linear(self, mod, x, delta, lin):
         """lin(norm(x + delta)); when the LUT sends this M to W8A8 the norm emits the int8 activations that
@@ -343,6 +350,7 @@ class Decoder(torch.nn.Module):
     def _prefill_body(self, tokens):
         b, s = tokens.shape
         x, delta = self._stack(self.embed[tokens], False)
+        delta = self._as_tensor(delta)
         last = self._norm(self.norm, x[:, -1:, :].contiguous(), None if delta is None else delta[:, -1:, :].contiguous())
         logits = last.reshape(b, -1) @ self.lm_head.t()
         self.mask.fill_(float('-inf'))

@@ -187,7 +187,13 @@ def rms_norm(x, weight, eps, residual_delta=None):
     m = x.numel() // k
     y = torch.empty_like(x)
     with _on(x.device):
-        if residual_delta is None:
+        if hasattr(residual_delta, 'peer_args'):
+            # the delta is still spread over a tensor-parallel group (tp.PendingPeerSum): summed while loaded
+            peer_in, peer_sig, world, rank = residual_delta.peer_args()
+            check(lib.kairos_add_rms_norm_peer(_chk(x, torch.float16, 'x'), peer_in, peer_sig, world, rank,
+                                               _chk(weight, torch.float16, 'weight'), y.data_ptr(), m, k, float(eps),
+                                               stream_ptr()), 'add_rms_norm_peer')
+        elif residual_delta is None:
             check(lib.kairos_rms_norm(_chk(x, torch.float16, 'x'), _chk(weight, torch.float16, 'weight'), y.data_ptr(),
                                       m, k, float(eps), stream_ptr()), 'rms_norm')
         else:
@@ -228,6 +234,14 @@ def rms_norm_quant(x, weight, eps, want_f16=False, residual_delta=None):
     xq = torch.empty(x.shape, dtype=torch.int8, device=x.device)
     sx = torch.empty((m,), dtype=torch.float16, device=x.device)
     y = torch.empty_like(x) if want_f16 else None
+    if hasattr(residual_delta, 'peer_args'):
+        peer_in, peer_sig, world, rank = residual_delta.peer_args()
+        with _on(x.device):
+            check(lib.kairos_rms_norm_quant_peer(_chk(x, torch.float16, 'x'), peer_in, peer_sig, world, rank,
+                                                 _chk(weight, torch.float16, 'weight'), None if y is None else y.data_ptr(),
+                                                 xq.data_ptr(), sx.data_ptr(), m, k, float(eps), stream_ptr()),
+                  'rms_norm_quant_peer')
+        return xq, sx, y
     with _on(x.device):
         check(lib.kairos_rms_norm_quant(_chk(x, torch.float16, 'x'),
                                         None if residual_delta is None else _chk(residual_delta, torch.float16, 'delta'),

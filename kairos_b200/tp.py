@@ -165,16 +165,47 @@ class PeerAllReduce:
         """The [m, n] fp16 view of the slot the next `reduce` will sum."""
         return self._slots[self.turn][:m * n].view(m, n)
 
-    def reduce(self, m, n, out=None):
+    def _launch(self, peer_in, m, n, out=None):
         if out is None:
             out = torch.empty((m, n), dtype=torch.float16, device=self.device)
-        self._check(self._lib.kairos_peer_allreduce_f16(self._in[self.turn], self._sig, self.world, self.rank,
-                                                        out.data_ptr(), m * n,
+        self._check(self._lib.kairos_peer_allreduce_f16(peer_in, self._sig, self.world, self.rank, out.data_ptr(), m * n,
                                                         torch.cuda.current_stream(self.device).cuda_stream),
                     'kairos_peer_allreduce_f16')
+        return out
+
+    def reduce(self, m, n, out=None):
+        """Sum the current slot over the group with the stand-alone kernel; flips the slot."""
+        out = self._launch(self._in[self.turn], m, n, out)
         self.turn ^= 1
         self.calls += 1
         return out
+
+    def defer(self, m, n, lead=None):
+        """Leave the sum to the RMSNorm that consumes the output (at most 128 tokens); flips the slot."""
+        pending = PendingPeerSum(self, self.turn, m, n, tuple(lead) if lead is not None else (m,))
+        self.turn ^= 1
+        self.calls += 1
+        return pending
+
+
+class PendingPeerSum:
+    """A row-parallel output whose sum over the group has not been formed yet: every rank's partial sits in its
+    peer-addressable slot.  The RMSNorm that consumes it (``ops.rms_norm`` / ``ops.rms_norm_quant`` with this
+    object as ``residual_delta``) sums the partials while it loads them, so the all-reduce costs no kernel of
+    its own; `materialize()` forms the sum with the stand-alone kernel instead.  Consume exactly once, in the
+    same order on every rank."""
+
+    def __init__(self, ar, turn, m, n, lead):
+        self.ar, self.turn, self.m, self.n, self.lead = ar, turn, m, n, lead
+        self.done = False
+
+    def peer_args(self):
+        assert not self.done, 'a pending peer sum is consumed once'
+        self.done = True
+        return self.ar._in[self.turn], self.ar._sig, self.ar.world, self.ar.rank
+
+    def materialize(self):
+        return self.ar._launch(self.peer_args()[0], self.m, self.n).view(*self.lead, self.n)
 
 
 class ColumnParallelLinear(torch.nn.Module):

@@ -97,9 +97,22 @@ def _decoder_worker(rank, world, port, out):
     torch.cuda.synchronize()
     gathered = [torch.empty_like(graphed) for _ in range(world)]
     dist.all_gather(gathered, graphed)
+    # the same step with the peer sum as a kernel of its own instead of inside the RMSNorm, and through NCCL
+    assert model.peer_ar is not None and model.fuse_peer_sum
+    model.release_graphs()
+    model.fuse_peer_sum = False
+    model.allocate(2, 64)
+    unfused = model.generate(tokens, 6, use_graph=True)
+    model.release_graphs()
+    model.peer_ar = None
+    model.allocate(2, 64)
+    by_nccl = model.generate(tokens, 6, use_graph=True)
+    torch.cuda.synchronize()
     if rank == 0:
         out['eager'] = eager.cpu().numpy()
         out['graphed'] = graphed.cpu().numpy()
+        out['unfused'] = unfused.cpu().numpy()
+        out['by_nccl'] = by_nccl.cpu().numpy()
         out['ranks_agree'] = all(torch.equal(g, graphed) for g in gathered)
         out['status'] = kb.runtime.device_status()
     model.release_graphs()      # graphs with captured collectives must be gone before the group is destroyed
@@ -111,13 +124,17 @@ def _decoder_worker(rank, world, port, out):
 def test_two_gpu_tensor_parallel_decoder_graph_matches_eager():
     """A two-rank tensor-parallel decoder (sharded heads and inner channels, all-reduce after o_proj and
     down_proj): the CUDA-graph path with the collectives captured gives the eager path's tokens, and every
-    rank ends with the same tokens."""
+    rank ends with the same tokens.  Small row-parallel outputs are summed over NVLink peer memory inside the
+    RMSNorm that consumes them; the stand-alone peer kernel and NCCL give the same tokens."""
     world = 2
     mgr = mp.Manager()
     out = mgr.dict()
     mp.spawn(_decoder_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert out['ranks_agree']
     assert np.array_equal(out['eager'], out['graphed'])
+    # sum inside the RMSNorm == stand-alone peer kernel == NCCL (two ranks: one fp16 rounding of a + b either way)
+    assert np.array_equal(out['graphed'], out['unfused'])
+    assert np.array_equal(out['graphed'], out['by_nccl'])
     assert out['status'] == 0
 
 
