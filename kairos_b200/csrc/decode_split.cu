@@ -215,10 +215,17 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
     const uint32_t ones = 0x3c003c00u;      // half2(1, 1)
     const __half2 k16th = __half2half2(__ushort_as_half(0x2c00));   // 1/16
     bool ok = true;
-    int s = 0, fs = kStages - 1;            // stage read / stage refilled in this iteration
     uint32_t parity = 0;
+    // The loop over the warp's groups is unrolled by the ring depth: the stage read (s) and the stage refilled
+    // (fs, the one read in the previous iteration) are then compile-time constants, and so are all shared-memory
+    // offsets and barrier addresses of an iteration.
 #pragma unroll 1
-    for (int it = 0; it < n_it; ++it) {
+    for (int it0 = 0; it0 < n_it && ok; it0 += kStages, parity ^= 1u) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+        const int it = it0 + s;
+        if (it >= n_it) break;
+        const int fs = (s + kStages - 1) % kStages;
         // refill the slot read in the previous iteration: every lane is done with it
         __syncwarp();
         if (it + kStages - 1 < n_it) {
@@ -236,8 +243,6 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
         }
         if (!mbar_wait(&full[s], parity, abort_flag)) { ok = false; break; }
         const uint32_t so = (uint32_t)(s * kStageBytes);
-        if (++s == kStages) { s = 0; parity ^= 1u; }
-        if (++fs == kStages) fs = 0;
 
         // The lane's 32 activations of token g (+ 8 nt) as 16 words, word 4 b + c = k 8 b + 2 c (+1).  The
         // words of the odd nibbles (b = 1, 3) are scaled by 1/16 here, because those nibbles enter the MMA
@@ -320,6 +325,7 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
                 }
         }
     }
+    }
     __syncwarp();
 
     // ---- the K slices of the CTA's warps meet in shared memory (each warp's slab: start of its ring) ----
@@ -388,6 +394,9 @@ static SplitShape split_shape(int N, int K, int rows) {
     s.cluster = 1;
     while (s.cluster < 4 && 2 * tiles * s.cluster < 5 * sms) s.cluster *= 2;
     if (s.cluster == 4 && tiles * 4 < sms) s.cluster = 8;
+    // long K (64 groups or more): two slices pay even when the row tiles alone would fill the GPU -- each warp still
+    // has a long run, and twice the warps hide more latency (K = 8192, N = 14336, M = 1: 20.5 -> 17.6 us)
+    if (s.cluster == 1 && G >= 64 && 2 * tiles <= 7 * sms) s.cluster = 2;
     while (s.cluster > 1 && G < s.cluster * s.warps) s.cluster /= 2;
     if (s.cluster > G) s.cluster = G;
     s.gpc = (G + s.cluster - 1) / s.cluster;
@@ -485,7 +494,8 @@ extern "C" int kairos_w4a16_decode(const void* X, const void* qweight, const voi
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     // Row blocks per warp: four (64 weight rows share one fetch of the activations) once the activations
     // are a noticeable part of the traffic and the matrix still yields enough row tiles, else two.
-    const bool rb4 = M <= 8 ? (M > 4 && N >= 4096) : (M <= 16 && N >= 2048 && N < 8192);
+    // (measured: M = 4 gains 10-20 % from four row blocks on matrices of 7168 rows or more, loses below)
+    const bool rb4 = M <= 8 ? ((M > 4 && N >= 4096) || (M > 2 && N >= 7168)) : (M <= 16 && N >= 2048 && N < 8192);
 #define KAIROS_SPLIT(NT, RB, XR) launch_split<NT, RB, XR>(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, st)
     if (M <= 1) return rb4 ? KAIROS_SPLIT(1, 4, 1) : KAIROS_SPLIT(1, 2, 1);
     if (M <= 2) return rb4 ? KAIROS_SPLIT(1, 4, 2) : KAIROS_SPLIT(1, 2, 2);

@@ -186,6 +186,26 @@ def _peer_allreduce_worker(rank, world, port, out):
         graph.replay()
         torch.cuda.synchronize()
         ok = ok and all(torch.equal(o, w) for o, w in zip(outs, wants))
+    # the sum folded into the RMSNorm that consumes it == stand-alone sum, then the norm with a local delta
+    from kairos_b200 import ops
+    for (m, k, quant) in [(1, 512, False), (5, 4096, True), (64, 1024, False), (24, 8192, True)] * 2:
+        part = ar.partial(m, k)
+        part.copy_(torch.randn((m, k), generator=gen, device=dev, dtype=torch.float32).half())
+        want_delta = expected(part)
+        x0 = torch.randn((m, k), generator=torch.Generator(device=dev).manual_seed(7), device=dev, dtype=torch.float32).half()
+        w = torch.randn((k,), generator=torch.Generator(device=dev).manual_seed(8), device=dev, dtype=torch.float32).half()
+        xa, xb = x0.clone(), x0.clone()
+        pending = ar.defer(m, k)
+        if quant:
+            qa, sa, ya = ops.rms_norm_quant(xa, w, 1e-5, want_f16=True, residual_delta=pending)
+            qb, sb, yb = ops.rms_norm_quant(xb, w, 1e-5, want_f16=True, residual_delta=want_delta)
+            same = torch.equal(qa, qb) and torch.equal(sa, sb) and torch.equal(ya, yb)
+        else:
+            ya = ops.rms_norm(xa, w, 1e-5, residual_delta=pending)
+            yb = ops.rms_norm(xb, w, 1e-5, residual_delta=want_delta)
+            same = torch.equal(ya, yb)
+        torch.cuda.synchronize()
+        ok = ok and same and torch.equal(xa, xb)          # x += delta in place, both ways
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
