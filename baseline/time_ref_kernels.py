@@ -2,7 +2,7 @@
 """Same-box GPU baseline: the reference's own CUDA kernels, rebuilt unmodified for sm_100a by
 baseline/build_ref_kernels.sh, timed beside this library's kernels on the points of the benchmark sweep.
 
-    python baseline/time_ref_kernels.py > gpurun_out/ref_kernels.jsonl
+    python baseline/time_ref_kernels.py > ref_kernels.jsonl
 
 Protocol: the reference's `timer` (utils/perf_eval.py:21-34): CUDA events around n back-to-back eager calls
 after warm-up, one set of weights (so small weights may sit in L2, for both arms alike).  Each arm runs the

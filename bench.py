@@ -413,8 +413,16 @@ def run_gpu_arm(args):
     # One pass of the sweep.  Row-parallel shapes come first and write their 14 outputs into ONE flat buffer
     # each, so a shape's partial sums cross NVLink in a single all-reduce, issued on a second stream: it runs
     # while the following shapes compute.  The whole pass, collectives included, is one CUDA graph.
+    # With `--tp-collective reducescatter` (the default) the sum is left sharded over the tokens (rank r keeps rows
+    # r * T / t .. (r + 1) * T / t of the shape's T = 16384 token rows: the sequence-sharded layout a following norm
+    # or residual addition consumes under sequence parallelism), which moves half the bytes of an all-reduce;
+    # `allreduce` leaves the full sum on every rank.  The run reports both step times.
     order = sorted(range(len(SHAPES_KN)), key=lambda li: not reduced[li])
-    flat = {li: torch.empty((sum(M_LIST), shapes[li][0]), dtype=torch.float16, device=device) for li in order}
+    rows_pad = (sum(M_LIST) + world - 1) // world * world
+    flat = {li: torch.zeros((rows_pad, shapes[li][0]), dtype=torch.float16, device=device) for li in order}
+    shard = {li: torch.empty((rows_pad // world, shapes[li][0]), dtype=torch.float16, device=device)
+             for li in order if reduced[li]} if world > 1 else {}
+    tp_mode = {'collective': args.tp_collective}
     views = {}
     for li in order:
         off = 0
@@ -433,7 +441,10 @@ def run_gpu_arm(args):
             if reduced[li]:
                 comm.wait_stream(main)
                 with torch.cuda.stream(comm):
-                    dist.all_reduce(flat[li], op=dist.ReduceOp.SUM)
+                    if tp_mode['collective'] == 'reducescatter':
+                        dist.reduce_scatter_tensor(shard[li], flat[li], op=dist.ReduceOp.SUM)
+                    else:
+                        dist.all_reduce(flat[li], op=dist.ReduceOp.SUM)
         if world > 1:
             main.wait_stream(comm)
 
@@ -450,11 +461,21 @@ def run_gpu_arm(args):
                 one_pass()
             graph.replay()
             torch.cuda.synchronize()
-            return graph.replay, 'cuda-graph' + (' (all-reduces captured, second stream)' if world > 1 else ''), graph
+            return graph.replay, 'cuda-graph' + (f" ({tp_mode['collective']} of the row-parallel shapes captured, second "
+                                                 'stream)' if world > 1 else ''), graph
         except Exception as exc:       # keep measuring, say why the graph was not used
             torch.cuda.synchronize()
             return one_pass, f'eager ({label}: graph capture failed: {type(exc).__name__})', None
 
+    ms_other = None
+    if world > 1:
+        # the other collective first, for the record; the headline uses args.tp_collective
+        tp_mode['collective'] = 'allreduce' if args.tp_collective == 'reducescatter' else 'reducescatter'
+        other_fn, _, other_graph = capture('other collective')
+        ms_other, _ = timed_blocks(torch, dist, world, device, other_fn, args.steps, args.warmup, min_seconds=0.3)
+        other_name = tp_mode['collective']
+        del other_fn, other_graph
+        tp_mode['collective'] = args.tp_collective
     step_fn, mode, graph = capture('warm')
 
     sampler = ClockSampler(local)
@@ -481,7 +502,16 @@ def run_gpu_arm(args):
     if world > 1:
         step_fn()
         torch.cuda.synchronize()
-        parity = check_parity(torch, dist, kb, rank, world, mods, reduced, views, xs_host, prof)
+        results = dict(views)
+        if args.tp_collective == 'reducescatter':
+            # rank 0's token rows hold the three checked M (offsets 0, 63, 1023; 16384 / world >= 2048 rows)
+            off = 0
+            for m in M_LIST:
+                for li in shard:
+                    results[(li, m)] = shard[li][off:off + m] if off + m <= rows_pad // world else None
+                off += m
+        parity = check_parity(torch, dist, kb, rank, world, mods, reduced, results, xs_host, prof)
+        parity['row_parallel_collective'] = args.tp_collective
 
     # kernels launched per pass: one GEMV/GEMM per point (+1 split-K reduce where split), +1 activation
     # quantization for W8A8, +1 conversion per cache miss
@@ -577,6 +607,10 @@ def run_gpu_arm(args):
     if parity is not None:
         out['parity_checked'] = parity['ok']
         out['parity'] = parity
+        out['config']['row_parallel_collective'] = (
+            'reduce-scatter over the token rows (sum left sequence-sharded; half the bytes of an all-reduce)'
+            if args.tp_collective == 'reducescatter' else 'all-reduce (full sum on every rank)')
+        out['ms_per_step_other_collective'] = {other_name: ms_other}
     if roof:
         out['roofline'] = roof
         out['roofline_gemv'] = roof_gemv
@@ -742,6 +776,8 @@ def main():
     ap.add_argument('--impl', default='kairos_b200', choices=['kairos_b200', 'reference'])
     ap.add_argument('--prof-iters', type=int, default=20)
     ap.add_argument('--no-llm', action='store_true', help='skip the TTFT/TPOT block (N = 1)')
+    ap.add_argument('--tp-collective', default='reducescatter', choices=['reducescatter', 'allreduce'],
+                    help='N > 1: how the partial outputs of the row-parallel shapes are summed')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference_arm(args)

@@ -188,7 +188,7 @@ def _peer_allreduce_worker(rank, world, port, out):
         ok = ok and all(torch.equal(o, w) for o, w in zip(outs, wants))
     # the sum folded into the RMSNorm that consumes it == stand-alone sum, then the norm with a local delta
     from kairos_b200 import ops
-    for (m, k, quant) in [(1, 512, False), (5, 4096, True), (64, 1024, False), (24, 8192, True)] * 2:
+    for (m, k, quant) in [(1, 512, False), (5, 4096, True), (64, 1024, False), (8, 8192, True)] * 2:
         part = ar.partial(m, k)
         part.copy_(torch.randn((m, k), generator=gen, device=dev, dtype=torch.float32).half())
         want_delta = expected(part)
