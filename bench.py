@@ -278,7 +278,8 @@ def timed_blocks(torch, dist, world, device, fn, steps, warmup, min_seconds=1.0,
     blocks, t_start = [], time.perf_counter()
     if mark:
         torch.cuda.profiler.start()      # lets `ncu --profile-from-start off` see exactly the timed steps
-    while len(blocks) < max_blocks and (not blocks or time.perf_counter() - t_start < min_seconds):
+    go_on = torch.ones(1, device=device) if world > 1 else None
+    while True:
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         for _ in range(steps):
@@ -286,6 +287,14 @@ def timed_blocks(torch, dist, world, device, fn, steps, warmup, min_seconds=1.0,
         e.record()
         e.synchronize()
         blocks.append(s.elapsed_time(e) / steps)
+        more = len(blocks) < max_blocks and time.perf_counter() - t_start < min_seconds
+        if world > 1:
+            # every rank must run the same number of blocks (fn holds collectives): rank 0's clock decides
+            go_on.fill_(1.0 if more else 0.0)
+            dist.broadcast(go_on, src=0)
+            more = bool(go_on.item())
+        if not more:
+            break
     torch.cuda.synchronize()
     if mark:
         torch.cuda.profiler.stop()
@@ -467,6 +476,11 @@ def run_gpu_arm(args):
             torch.cuda.synchronize()
             return one_pass, f'eager ({label}: graph capture failed: {type(exc).__name__})', None
 
+    def note(msg):
+        if rank == 0 and os.environ.get('KAIROS_BENCH_VERBOSE'):
+            print(f'[bench {time.strftime("%H:%M:%S")}] {msg}', file=sys.stderr, flush=True)
+
+    note('layers, inputs and LUTs ready')
     ms_other = None
     if world > 1:
         # the other collective first, for the record; the headline uses args.tp_collective
@@ -476,7 +490,9 @@ def run_gpu_arm(args):
         other_name = tp_mode['collective']
         del other_fn, other_graph
         tp_mode['collective'] = args.tp_collective
+        note(f'other collective timed: {ms_other:.3f} ms per step')
     step_fn, mode, graph = capture('warm')
+    note('warm pass captured: ' + mode)
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -487,8 +503,11 @@ def run_gpu_arm(args):
     clocks = sampler.stop() if rank == 0 else None
     n_timed_steps = len(blocks) * args.steps
 
+    note(f'timed region done: {ms_step:.3f} ms per step')
     ms_eager, _ = timed_blocks(torch, dist, world, device, one_pass, max(1, args.steps // 4), 1, min_seconds=0.2)
+    note('eager pass timed')
     ms_e2e, _ = timed_blocks(torch, dist, world, device, one_pass_host, max(1, args.steps // 4), 1, min_seconds=0.5)
+    note('host-buffer pass timed')
 
     # ---- the cold regime: same pass, nothing cached (every W8A8 / W8A16 / FP16 call converts first) ----
     use('cold')
@@ -510,7 +529,9 @@ def run_gpu_arm(args):
                 for li in shard:
                     results[(li, m)] = shard[li][off:off + m] if off + m <= rows_pad // world else None
                 off += m
+        note('cold regime timed; checking parity')
         parity = check_parity(torch, dist, kb, rank, world, mods, reduced, results, xs_host, prof)
+        note('parity checked')
         parity['row_parallel_collective'] = args.tp_collective
 
     # kernels launched per pass: one GEMV/GEMM per point (+1 split-K reduce where split), +1 activation
