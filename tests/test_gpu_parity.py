@@ -168,7 +168,7 @@ def test_gemv(kb, m, k, n):
                                    (6, 4096, 4104), (7, 2048, 8200), (12, 4096, 2072), (1, 28672, 8192), (2, 8192, 28672),
                                    (8, 384, 1032), (3, 128, 8),
                                    # long K with row tiles enough for the GPU: two K slices all the same; four row blocks at M = 3, 4
-                                   (1, 8192, 11872), (4, 8192, 7168), (3, 4096, 14336)])
+                                   (1, 8192, 11872), (4, 8192, 7168), (3, 4096, 14336), (2, 4096, 14336), (1, 256, 14344)])
 def test_decode_mma(kb, m, k, n):
     _, ops, _ = kb
     x, _, res = case(m, k, n, seed=m)
