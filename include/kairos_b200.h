@@ -129,6 +129,10 @@ int kairos_w4a16_small_batch(const void* X_f16, const void* qweight, const void*
  * the problem is not split; then `workspace` may be null).  Contents need no initialisation.
  * Calls that share a workspace must be ordered (same stream). */
 size_t kairos_gemm_workspace_bytes(int M, int N, int K);
+/* Diagnostic: the tiling the one-CTA tensor-core GEMM would use for W8A8 (int8 != 0) or FP16 operands of this
+ * shape on the current device: tokens per tile (16..256; weight rows per tile are always 128), the number of K
+ * runs a tile is split into (1 = no split-K scratch needed) and the number of output tiles.  Nothing is launched. */
+int kairos_gemm_plan_query(int M, int N, int K, int int8, int* token_tile, int* k_runs, int* tiles);
 
 /* Y = X . dequant(W)^T (+bias): tcgen05 f16 MMA, uint4 dequantized in shared memory (N % 8 == 0).
  * Replaces gemm_forward_cuda_new

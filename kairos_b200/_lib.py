@@ -31,6 +31,8 @@ SIGNATURES = {
     'kairos_w4a16_decode': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p]),
     'kairos_w4a16_small_batch': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p]),
     'kairos_gemm_workspace_bytes': (c_size_t, [c_int, c_int, c_int]),
+    'kairos_gemm_plan_query': (c_int, [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int),
+                                       ctypes.POINTER(c_int)]),
     'kairos_w4a16_gemm': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
     'kairos_w4a16_gemm_noalloc': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p]),
     'kairos_w8a16_gemm': (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),

@@ -1248,6 +1248,15 @@ extern "C" void kairos_debug_trace(void* device_buffer) { kairos::g_trace = stat
 
 extern "C" size_t kairos_gemm_workspace_bytes(int M, int N, int K) { return kairos::gemm_workspace_bytes(M, N, K); }
 
+extern "C" int kairos_gemm_plan_query(int M, int N, int K, int int8, int* token_tile, int* k_runs, int* tiles) {
+    if (M <= 0 || N <= 0 || K <= 0 || (K % 128) != 0 || !token_tile || !k_runs || !tiles) return KAIROS_ERR_ARG;
+    const kairos::Plan pl = kairos::make_plan(M, N, K, int8 != 0, ~(size_t)0, false, true);
+    *token_tile = pl.bt;
+    *k_runs = pl.splits;
+    *tiles = pl.n_tiles * pl.m_tiles;
+    return KAIROS_OK;
+}
+
 extern "C" int kairos_w4a16_gemm(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
                                  const void* bias, void* Y, int M, int N, int K, void* workspace,
                                  size_t workspace_bytes, kairos_stream_t stream) {

@@ -52,6 +52,42 @@ def test_argument_validation_needs_no_device():
     assert L.kairos_gemm_workspace_bytes(8192, 4096, 4096) == 0
 
 
+def test_gemm_plan_invariants_and_the_measured_choices():
+    """The one-CTA GEMM's plan (token tile, K runs) for the TMA-fed modes: structural invariants over a grid of
+    shapes, and the choices the cost model was fitted to make (graph-timed on B200, 148 SMs assumed without a GPU)."""
+    import ctypes
+    L = _lib.lib
+
+    def plan(m, n, k, int8=1):
+        bt, runs, tiles = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        assert L.kairos_gemm_plan_query(m, n, k, int8, ctypes.byref(bt), ctypes.byref(runs), ctypes.byref(tiles)) == 0
+        return bt.value, runs.value, tiles.value
+
+    for int8 in (0, 1):
+        for k, n in [(4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096), (512, 256), (8192, 28672)]:
+            for m in (1, 16, 17, 64, 65, 100, 128, 192, 256, 300, 512, 777, 1024, 2048, 8192):
+                bt, runs, tiles = plan(m, n, k, int8)
+                assert bt in (16, 32, 64, 128, 256) and runs >= 1
+                assert tiles == -(-n // 128) * -(-m // bt)
+                assert bt >= min(m, 16) and (m <= 64 or bt >= 64)
+                assert runs == 1 or tiles * runs <= 148           # a split never makes more units than SMs
+                need = L.kairos_gemm_workspace_bytes(m, n, k)
+                assert need >= (tiles * runs * bt * 128 * 4 if runs > 1 else 0)
+    assert L.kairos_gemm_plan_query(0, 128, 128, 1, None, None, None) == -8
+    # measured winners (W8A8): unsplit 128- / 64-token tiles where 256-token tiles leave SMs idle ...
+    assert plan(512, 4096, 4096)[:2] == (128, 1)
+    assert plan(256, 4096, 4096)[:2] == (64, 1)
+    assert plan(2048, 1024, 4096)[:2] == (128, 1)
+    assert plan(1024, 1024, 4096)[:2] == (64, 1)
+    # ... 256-token tiles once they fill the GPU ...
+    assert plan(1024, 4096, 4096)[:2] == (256, 1)
+    assert plan(256, 14336, 4096)[:2] == (256, 1)
+    # ... and a K split only for very few tiles or long K
+    assert plan(128, 1024, 4096)[1] > 1
+    assert plan(128, 4096, 14336)[:2] == (128, 4)
+    assert plan(128, 4096, 4096)[1] == 1
+
+
 def test_native_lut_known_answers():
     cases = json.load(open(os.path.join(GOLDEN, 'lut_known_answers.json')))
     for c in cases:
