@@ -699,7 +699,7 @@ def check_parity(torch, dist, kb, rank, world, mods, reduced, views, xs_host, pr
 PROFILE_TRAFFIC = {
     'umma_gemm_pair_kernel<int8> (cta_group::2, 256x256)': (152148992 + 191360768, 'profiles/umma_gemm_pair_int8_M8192_K4096_N14336.md'),
     'umma_gemm_pair_kernel<f16> (cta_group::2, 256x256)': (372429056 + 216130304, 'profiles/umma_gemm_pair_f16_M8192_K4096_N14336.md'),
-    'decode': (31227392, 'profiles/decode_split_M1_K4096_N14336.md'),
+    'decode': (31241216, 'profiles/decode_split_M1_K4096_N14336.md'),
 }
 
 
