@@ -179,3 +179,18 @@ def test_quantize_model_swaps_decoder_linears():
     assert torch.equal(m2.model.layers[0].mlp.up_proj.qweight, m.model.layers[0].mlp.up_proj.qweight)
     with pytest.raises(ValueError):
         quantize_model(_TinyModel(), quant_strategy='W4A8Linear')
+
+
+def test_first_argmax_is_torch_argmax():
+    """The decoder's two-level argmax returns torch's answer (first maximum), ties and odd vocabularies included."""
+    from kairos_b200.llm import first_argmax
+    g = torch.Generator().manual_seed(0)
+    for rows, vocab in [(2, 128256), (3, 152064), (1, 1000), (4, 1024), (5, 2048)]:
+        x = torch.randn(rows, vocab, generator=g).half()
+        assert torch.equal(first_argmax(x), x.argmax(-1, keepdim=True))
+        top = x.max(dim=-1).values
+        for r in range(rows):
+            x[r, torch.randint(0, vocab, (5,), generator=g)] = top[r]
+        assert torch.equal(first_argmax(x), x.argmax(-1, keepdim=True))
+    z = torch.zeros(2, 128256).half()
+    assert torch.equal(first_argmax(z), z.argmax(-1, keepdim=True))
