@@ -119,6 +119,13 @@ int kairos_w4a16_gemv(const void* X_f16, const void* qweight, const void* scales
  * reference runs batch 17..32 through the same template). */
 int kairos_w4a16_decode(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
                         const void* bias_f16_or_null, void* Y_f16, int M, int N, int K, kairos_stream_t stream);
+/* The same kernel with the epilogue of a gated MLP (no counterpart in the reference, whose model code leaves
+ * SiLU(gate) * up to torch): the N = 2 I weight rows are the gate and up projections stacked in the BLOCKED order
+ * (16 gate rows, their 16 up rows, the next 16 gate rows, ...; N % 32 == 0), so a row tile of the kernel holds
+ * matching rows, and Y_act [M, I] = half(half(silu(gate)) * up) is written instead of the [M, 2 I] activation:
+ * bit-identical to kairos_w4a16_decode followed by kairos_silu_mul_blocked, one kernel and one round trip less. */
+int kairos_w4a16_decode_silu(const void* X_f16, const void* qweight, const void* scales, const void* scaled_zeros,
+                             const void* bias_or_null, void* Y_act_f16, int M, int N, int K, kairos_stream_t stream);
 
 /* Kernel id 1 as the switched linear runs it: the decode kernel when N % 8 == 0, else the CUDA-core
  * kernel; 1 <= M <= 32.  This is the drop-in for gemv_forward_cuda_new. */
@@ -191,6 +198,12 @@ int kairos_add_rms_norm(void* X_f16_inout, const void* H_f16, const void* W_f16,
                         kairos_stream_t stream);
 /* Y[m,i] = silu(GU[m,i]) * GU[m,I+i] for the fused gate|up activation GU [M, 2I]; I % 8 == 0 */
 int kairos_silu_mul(const void* GU_f16, void* Y_f16, int M, int I, kairos_stream_t stream);
+/* kairos_silu_mul / kairos_silu_mul_quant for a [M, 2 I] activation in the blocked order (gate of inner channel i at
+ * column 32 (i / 16) + i % 16, up 16 columns further; I % 16 == 0): what a gate|up linear with blocked weight rows
+ * produces when it does not run the fused decode kernel. */
+int kairos_silu_mul_blocked(const void* GU_f16, void* Y_f16, int M, int I, kairos_stream_t stream);
+int kairos_silu_mul_quant_blocked(const void* GU_f16, void* Y_or_null, void* Xq_i8, void* sx_f16, int M, int I,
+                                  kairos_stream_t stream);
 /* The same two operators emitting the precision a following W8A8 linear consumes: per-token int8 Xq + fp16
  * scale sx, bit-identical to kairos_act_quant_i8 applied to the fp16 result; the fp16 tensor itself is
  * written only when Y is given.  With H given, X <- X + H first (as in kairos_add_rms_norm).

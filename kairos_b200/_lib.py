@@ -29,6 +29,9 @@ SIGNATURES = {
     'kairos_awq_to_qserve': (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     'kairos_w4a16_gemv': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p]),
     'kairos_w4a16_decode': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p]),
+    'kairos_w4a16_decode_silu': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p]),
+    'kairos_silu_mul_blocked': (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    'kairos_silu_mul_quant_blocked': (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p]),
     'kairos_w4a16_small_batch': (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_void_p]),
     'kairos_gemm_workspace_bytes': (c_size_t, [c_int, c_int, c_int]),
     'kairos_gemm_plan_query': (c_int, [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int),

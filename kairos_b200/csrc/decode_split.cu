@@ -47,6 +47,8 @@ struct SplitParams {
     int M, N, K, G;   // G = K / 128 quantization groups
     int C;            // CTAs per cluster = K slices of a row tile
     int gpc;          // groups per K slice
+    int silu;         // 1: the weight rows are gate / up rows in the blocked order (16 gate rows, their 16 up rows,
+                      // ...) and Y is [M, N / 2]: Y[m, i] = half(half(silu(gate_i)) * up_i), the epilogue of a gated MLP
     int* status;      // raised when a bounded wait runs out
 };
 
@@ -358,8 +360,35 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
         p.Y[(size_t)tok * p.N + n] = y;
     };
     const int n_out = kRows * min(8 * NT, (p.M + 1) & ~1);   // token columns that exist (pairs)
+    // Gated-MLP epilogue: output o2 = (token, channel r of the tile's kRows / 2 inner channels) takes the gate row
+    // 32 (r / 16) + r % 16 of the tile and the up row 16 further.  Same arithmetic as the stand-alone kernel: the
+    // two linear outputs rounded to fp16 (+ bias), SiLU in fp32 rounded to fp16, fp16 product.
+    auto store_gated = [&](int o2, float gv, float uv) {
+        const int tok = o2 / (kRows / 2), r = o2 % (kRows / 2);
+        const int ng = row0 + 32 * (r >> 4) + (r & 15);
+        if (tok >= p.M || ng + 16 >= p.N || failed) return;
+        __half gh = __float2half_rn(gv), uh = __float2half_rn(uv);
+        if (p.bias) {
+            gh = __hadd(gh, p.bias[ng]);
+            uh = __hadd(uh, p.bias[ng + 16]);
+        }
+        const float f = __half2float(gh);
+        const __half sl = __float2half_rn(f / (1.f + __expf(-f)));
+        p.Y[(size_t)tok * (p.N / 2) + row0 / 2 + r] = __hmul(sl, uh);
+    };
+    auto gate_index = [&](int o2) {
+        const int tok = o2 / (kRows / 2), r = o2 % (kRows / 2);
+        return tok * kRows + 32 * (r >> 4) + (r & 15);
+    };
     if (!clustered) {
-        for (int o = threadIdx.x; o < n_out; o += blockDim.x) store_out(o, cta_sum(o));
+        if (p.silu) {
+            for (int o2 = threadIdx.x; o2 < n_out / 2; o2 += blockDim.x) {
+                const int og = gate_index(o2);
+                store_gated(o2, cta_sum(og), cta_sum(og + 16));
+            }
+        } else {
+            for (int o = threadIdx.x; o < n_out; o += blockDim.x) store_out(o, cta_sum(o));
+        }
         return;
     }
     // ---- the K slices of the cluster meet in the shared memory of its first CTA ----
@@ -369,10 +398,18 @@ __global__ void __launch_bounds__(32 * kDsMaxWarps, SplitCfg<NT, RB, XR>::kMinBl
     cluster_arrive();
     cluster_wait();
     if (crank != 0) return;
-    for (int o = threadIdx.x; o < n_out; o += blockDim.x) {
+    auto cluster_sum = [&](int o) {
         float v = 0.f;
         for (int c = 0; c < p.C; ++c) v += gather[c * kOut + o];
-        store_out(o, v);
+        return v;
+    };
+    if (p.silu) {
+        for (int o2 = threadIdx.x; o2 < n_out / 2; o2 += blockDim.x) {
+            const int og = gate_index(o2);
+            store_gated(o2, cluster_sum(og), cluster_sum(og + 16));
+        }
+    } else {
+        for (int o = threadIdx.x; o < n_out; o += blockDim.x) store_out(o, cluster_sum(o));
     }
 }
 
@@ -411,7 +448,7 @@ static SplitShape split_shape(int N, int K, int rows) {
 
 template <int NT, int RB, int XR>
 static int launch_split(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
-                        const void* bias, void* Y, int M, int N, int K, cudaStream_t stream) {
+                        const void* bias, void* Y, int M, int N, int K, cudaStream_t stream, int silu) {
     using Cfg = SplitCfg<NT, RB, XR>;
     const SplitShape sh = split_shape(N, K, Cfg::kRows);
     SplitParams p;
@@ -424,6 +461,7 @@ static int launch_split(const void* X, const void* qweight, const void* scales, 
     p.M = M; p.N = N; p.K = K; p.G = K / kGroup;
     p.C = sh.cluster;
     p.gpc = sh.gpc;
+    p.silu = silu;
     p.status = device_status_word();
     if (!p.status) return KAIROS_ERR_CUDA;
     CUtensorMap tw, tx, ts, tz;
@@ -482,11 +520,11 @@ static int launch_split(const void* X, const void* qweight, const void* scales, 
 
 }  // namespace kairos
 
-/* Decode-side W4A16 on warp-level tensor-core instructions, 1 <= M <= 32 (N % 8 == 0). */
-extern "C" int kairos_w4a16_decode(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
-                                   const void* bias, void* Y, int M, int N, int K, kairos_stream_t stream) {
-    using namespace kairos;
-    if (M < 0 || M > 32 || N <= 0 || K <= 0 || (N % 8) != 0 || (K % kGroup) != 0) return KAIROS_ERR_SHAPE;
+namespace kairos {
+static int decode_entry(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
+                        const void* bias, void* Y, int M, int N, int K, kairos_stream_t stream, int silu) {
+    if (M < 0 || M > 32 || N <= 0 || K <= 0 || (N % 8) != 0 || (K % kGroup) != 0 || (silu && (N % 32) != 0))
+        return KAIROS_ERR_SHAPE;
     if (M == 0) return KAIROS_OK;
     if (!X || !qweight || !scales || !scaled_zeros || !Y || ((uintptr_t)X & 15) || ((uintptr_t)qweight & 15) ||
         ((uintptr_t)scales & 15) || ((uintptr_t)scaled_zeros & 15) || ((uintptr_t)Y & 1))
@@ -496,7 +534,7 @@ extern "C" int kairos_w4a16_decode(const void* X, const void* qweight, const voi
     // are a noticeable part of the traffic and the matrix still yields enough row tiles, else two.
     // (measured: M = 4 gains 10-20 % from four row blocks on matrices of 7168 rows or more, loses below)
     const bool rb4 = M <= 8 ? ((M > 4 && N >= 4096) || (M > 2 && N >= 7168)) : (M <= 16 && N >= 2048 && N < 8192);
-#define KAIROS_SPLIT(NT, RB, XR) launch_split<NT, RB, XR>(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, st)
+#define KAIROS_SPLIT(NT, RB, XR) launch_split<NT, RB, XR>(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, st, silu)
     if (M <= 1) return rb4 ? KAIROS_SPLIT(1, 4, 1) : KAIROS_SPLIT(1, 2, 1);
     if (M <= 2) return rb4 ? KAIROS_SPLIT(1, 4, 2) : KAIROS_SPLIT(1, 2, 2);
     if (M <= 4) return rb4 ? KAIROS_SPLIT(1, 4, 4) : KAIROS_SPLIT(1, 2, 4);
@@ -504,4 +542,17 @@ extern "C" int kairos_w4a16_decode(const void* X, const void* qweight, const voi
     if (M <= 16) return rb4 ? KAIROS_SPLIT(2, 4, 16) : KAIROS_SPLIT(2, 2, 16);
     return KAIROS_SPLIT(4, 2, 32);
 #undef KAIROS_SPLIT
+}
+}  // namespace kairos
+
+/* Decode-side W4A16 on warp-level tensor-core instructions, 1 <= M <= 32 (N % 8 == 0). */
+extern "C" int kairos_w4a16_decode(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
+                                   const void* bias, void* Y, int M, int N, int K, kairos_stream_t stream) {
+    return kairos::decode_entry(X, qweight, scales, scaled_zeros, bias, Y, M, N, K, stream, 0);
+}
+
+/* The same with the gated-MLP epilogue: N = 2 I stacked gate / up rows in the blocked order, Y_act [M, I]. */
+extern "C" int kairos_w4a16_decode_silu(const void* X, const void* qweight, const void* scales, const void* scaled_zeros,
+                                        const void* bias, void* Y_act, int M, int N, int K, kairos_stream_t stream) {
+    return kairos::decode_entry(X, qweight, scales, scaled_zeros, bias, Y_act, M, N, K, stream, 1);
 }

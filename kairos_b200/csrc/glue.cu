@@ -99,17 +99,29 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(__half* X, const __half* 
     }
 }
 
-// Y[m, i] = half( half(silu(gate)) * up ), gate = GU[m, i], up = GU[m, I + i]
+// Where gate and up of inner channel i sit in a row of the stacked activation [2 I]:
+//   plain layout    gate at i, up at I + i (the two weights stacked one after the other);
+//   blocked layout  16 gate channels, then their 16 up channels, and so on: gate at 32 (i / 16) + i % 16, up 16
+//                   further.  A row tile of the decode kernel (32 or 64 weight rows) then holds matching gate and
+//                   up rows, so that kernel can apply SiLU(gate) * up in its epilogue (kairos_w4a16_decode_silu).
+// In 16-byte chunks of 8 channels: chunk c of the result reads gate chunk gate_chunk(c) and up chunk up_chunk(c).
+__device__ __forceinline__ int gate_chunk(int c, int per_row, bool blocked) { return blocked ? 4 * (c >> 1) + (c & 1) : c; }
+__device__ __forceinline__ int up_chunk(int c, int per_row, bool blocked) {
+    return blocked ? 4 * (c >> 1) + (c & 1) + 2 : per_row + c;
+}
+
+// Y[m, i] = half( half(silu(gate)) * up )
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* __restrict__ GU, __half* __restrict__ Y, int M,
-                                                       int I) {
+                                                       int I, int blocked) {
     chain_release();
     chain_wait();
     const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;       // one 8-element chunk
     const int per_row = I >> 3;
     if (idx >= (long long)M * per_row) return;
     const int m = (int)(idx / per_row), c = (int)(idx % per_row);
-    const uint4 g4 = __ldcg(reinterpret_cast<const uint4*>(GU + (size_t)m * 2 * I) + c);
-    const uint4 u4 = __ldcg(reinterpret_cast<const uint4*>(GU + (size_t)m * 2 * I + I) + c);
+    const uint4* row = reinterpret_cast<const uint4*>(GU + (size_t)m * 2 * I);
+    const uint4 g4 = __ldcg(row + gate_chunk(c, per_row, blocked != 0));
+    const uint4 u4 = __ldcg(row + up_chunk(c, per_row, blocked != 0));
     const __half2* g = reinterpret_cast<const __half2*>(&g4);
     const __half2* u = reinterpret_cast<const __half2*>(&u4);
     uint4 o4;
@@ -227,21 +239,22 @@ __global__ void __launch_bounds__(256) rms_norm_quant_kernel(__half* X, const __
 // SiLU(gate) * up followed by the same per-token int8 quantization, one CTA per token.
 template <int R>
 __global__ void __launch_bounds__(256) silu_mul_quant_kernel(const __half* __restrict__ GU, __half* __restrict__ Y,
-                                                             int8_t* __restrict__ Xq, __half* __restrict__ sx, int I) {
+                                                             int8_t* __restrict__ Xq, __half* __restrict__ sx, int I,
+                                                             int blocked) {
     __shared__ float part[8];
     chain_release();
     chain_wait();
     const int token = blockIdx.x;
     const int chunks = I >> 3;
-    const uint4* gp = reinterpret_cast<const uint4*>(GU + (size_t)token * 2 * I);
-    const uint4* up = reinterpret_cast<const uint4*>(GU + (size_t)token * 2 * I + I);
+    const uint4* row = reinterpret_cast<const uint4*>(GU + (size_t)token * 2 * I);
     uint4 v[R];
     float amax = 0.f;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int c = threadIdx.x + r * 256;
         if (c < chunks) {
-            const uint4 g4 = __ldcg(gp + c), u4 = __ldcg(up + c);
+            const uint4 g4 = __ldcg(row + gate_chunk(c, chunks, blocked != 0));
+            const uint4 u4 = __ldcg(row + up_chunk(c, chunks, blocked != 0));
             const __half2* g = reinterpret_cast<const __half2*>(&g4);
             const __half2* u = reinterpret_cast<const __half2*>(&u4);
             uint4 o4;
@@ -405,17 +418,24 @@ extern "C" int kairos_rms_norm_quant_peer(void* X, const void* const* peer_in, v
     return run_rms_norm_quant(X, nullptr, W, Y_or_null, Xq, sx, M, K, eps, reinterpret_cast<cudaStream_t>(stream), &ps);
 }
 
-extern "C" int kairos_silu_mul(const void* GU, void* Y, int M, int I, kairos_stream_t stream) {
+static int run_silu_mul(const void* GU, void* Y, int M, int I, int blocked, kairos_stream_t stream) {
     using namespace kairos;
-    if (M < 0 || I <= 0 || (I % 8) != 0) return KAIROS_ERR_SHAPE;
+    if (M < 0 || I <= 0 || (I % 8) != 0 || (blocked && (I % 16) != 0)) return KAIROS_ERR_SHAPE;
     if (M == 0) return KAIROS_OK;
     if (!GU || !Y || ((uintptr_t)GU & 15) || ((uintptr_t)Y & 15)) return KAIROS_ERR_ALIGN;
     const long long chunks = (long long)M * (I / 8);
     const cudaError_t e = launch_chained(silu_mul_kernel, dim3((unsigned)((chunks + 255) / 256)), dim3(256), 0,
                                          reinterpret_cast<cudaStream_t>(stream), static_cast<const __half*>(GU),
-                                         static_cast<__half*>(Y), M, I);
+                                         static_cast<__half*>(Y), M, I, blocked);
     if (e != cudaSuccess) return note_cuda_error(e);
     return launch_status();
+}
+
+extern "C" int kairos_silu_mul(const void* GU, void* Y, int M, int I, kairos_stream_t stream) {
+    return run_silu_mul(GU, Y, M, I, 0, stream);
+}
+extern "C" int kairos_silu_mul_blocked(const void* GU, void* Y, int M, int I, kairos_stream_t stream) {
+    return run_silu_mul(GU, Y, M, I, 1, stream);
 }
 
 extern "C" int kairos_rope_kv(const void* QKV, const void* cos_table, const void* sin_table, const void* pos_dev_or_null,
@@ -446,8 +466,20 @@ extern "C" int kairos_rms_norm_quant(void* X, const void* H_or_null, const void*
     return run_rms_norm_quant(X, H_or_null, W, Y_or_null, Xq, sx, M, K, eps, reinterpret_cast<cudaStream_t>(stream));
 }
 
+static int run_silu_mul_quant(const void* GU, void* Y_or_null, void* Xq, void* sx, int M, int I, int blocked,
+                              kairos_stream_t stream);
+
 extern "C" int kairos_silu_mul_quant(const void* GU, void* Y_or_null, void* Xq, void* sx, int M, int I,
                                      kairos_stream_t stream) {
+    return run_silu_mul_quant(GU, Y_or_null, Xq, sx, M, I, 0, stream);
+}
+extern "C" int kairos_silu_mul_quant_blocked(const void* GU, void* Y_or_null, void* Xq, void* sx, int M, int I,
+                                             kairos_stream_t stream) {
+    return run_silu_mul_quant(GU, Y_or_null, Xq, sx, M, I, 1, stream);
+}
+
+static int run_silu_mul_quant(const void* GU, void* Y_or_null, void* Xq, void* sx, int M, int I, int blocked,
+                              kairos_stream_t stream) {
     using namespace kairos;
     if (M < 0 || I <= 0 || (I % 16) != 0 || I > 8 * 256 * 16) return KAIROS_ERR_SHAPE;
     if (M == 0) return KAIROS_OK;
@@ -460,9 +492,9 @@ extern "C" int kairos_silu_mul_quant(const void* GU, void* Y_or_null, void* Xq, 
     __half* s = static_cast<__half*>(sx);
     const int per = (I / 8 + 255) / 256;
     cudaError_t e;
-    if (per <= 4) e = launch_chained(silu_mul_quant_kernel<4>, dim3(M), dim3(256), 0, st, gu, y, q, s, I);
-    else if (per <= 8) e = launch_chained(silu_mul_quant_kernel<8>, dim3(M), dim3(256), 0, st, gu, y, q, s, I);
-    else e = launch_chained(silu_mul_quant_kernel<16>, dim3(M), dim3(256), 0, st, gu, y, q, s, I);
+    if (per <= 4) e = launch_chained(silu_mul_quant_kernel<4>, dim3(M), dim3(256), 0, st, gu, y, q, s, I, blocked);
+    else if (per <= 8) e = launch_chained(silu_mul_quant_kernel<8>, dim3(M), dim3(256), 0, st, gu, y, q, s, I, blocked);
+    else e = launch_chained(silu_mul_quant_kernel<16>, dim3(M), dim3(256), 0, st, gu, y, q, s, I, blocked);
     if (e != cudaSuccess) return note_cuda_error(e);
     return launch_status();
 }

@@ -21,7 +21,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 from . import ops
-from .dynamic_linear import DynamicLinear
+from .dynamic_linear import COMP_TYPE_NAME, DynamicLinear
 from .perf_profiler import Profiler
 from .quant_model import quantize_model
 
@@ -174,6 +174,9 @@ class Decoder(torch.nn.Module):
         self.device = torch.device(device)
         self.fuse, self.glue = fuse_linears, glue
         self.fuse_quant = True       # let RMSNorm / SiLU*up emit int8 when the next linear runs W8A8
+        # gate and up rows of the stacked weight in blocks of 16 (SiLU * up inside the decode kernel's epilogue)
+        self.blocked_gate_up = os.environ.get('KAIROS_BLOCKED_GATE_UP', '1') != '0' and cfg.inter % 16 == 0
+        self.fuse_gate_silu = True   # False: the same layout, SiLU * up as a kernel of its own (for comparison)
         n_layers = cfg.layers if layers is None else layers
         gen = torch.Generator(device=self.device).manual_seed(seed)
         self.model = _Inner()
@@ -347,11 +350,32 @@ class Decoder(torch.nn.Module):
         if not self.fuse:
             h = self._norm(layer.post_attention_layernorm, x, attn_out)
             return self._row_parallel(m.down_proj, F.silu(m.gate_proj(h)) * m.up_proj(h))
-        gu = self._norm_then_linear(layer.post_attention_layernorm, x, attn_out, m.gate_up_proj)
-        if self.glue == 'cuda' and self.fuse_quant and m.down_proj.wants_int8(b * s):
-            aq, sa, _ = ops.silu_mul_quant(gu)
+        # The rows of the stacked gate|up weight are read in the BLOCKED order (16 gate rows, their 16 up rows,
+        # ...; for random weights that is only a naming of rows, a checkpoint loader would interleave them),
+        # so that the decode kernel can apply SiLU(gate) * up in its epilogue.
+        blocked = self.blocked_gate_up
+        tokens = b * s
+        down_q8 = self.glue == 'cuda' and self.fuse_quant and m.down_proj.wants_int8(tokens)
+        gup = m.gate_up_proj
+        if (blocked and self.glue == 'cuda' and self.fuse_gate_silu and not down_q8 and tokens <= 32
+                and gup.out_features % 32 == 0 and gup.bias is None
+                and not gup.wants_int8(tokens) and gup.comp_type == COMP_TYPE_NAME['w4a16_gemv']):
+            # (wants_int8 refreshed gup.comp_type for this token count)
+            h = self._norm(layer.post_attention_layernorm, x, attn_out)
+            act = ops.decode_silu_forward(h, gup.qweight, gup.scales, gup.scaled_zeros, tokens, gup.out_features,
+                                          gup.in_features).view(b, s, -1)
+            return self._row_parallel(m.down_proj, act)
+        gu = self._norm_then_linear(layer.post_attention_layernorm, x, attn_out, gup)
+        if down_q8:
+            aq, sa, _ = ops.silu_mul_quant(gu, blocked=blocked)
             return self._row_parallel(m.down_proj, None, (aq, sa))
-        act = ops.silu_mul(gu) if self.glue == 'cuda' else F.silu(gu[..., :cfg.inter]) * gu[..., cfg.inter:]
+        if self.glue == 'cuda':
+            act = ops.silu_mul(gu, blocked=blocked)
+        elif blocked:
+            pairs = gu.view(*gu.shape[:-1], cfg.inter // 16, 2, 16)
+            act = (F.silu(pairs[..., 0, :]) * pairs[..., 1, :]).reshape(*gu.shape[:-1], cfg.inter)
+        else:
+            act = F.silu(gu[..., :cfg.inter]) * gu[..., cfg.inter:]
         return self._row_parallel(m.down_proj, act)
 
     def _stack(self, x, decode):

@@ -126,6 +126,19 @@ def decode_forward(in_feats, kernel, scaling_factors, zeros, m, n, k, bias=None)
     return out
 
 
+def decode_silu_forward(in_feats, kernel, scaling_factors, zeros, m, n, k, bias=None):
+    """Gate|up linear (n = 2 I weight rows in the blocked order) with SiLU(gate) * up applied in the decode kernel's
+    epilogue, 1 <= m <= 32: returns [m, I]."""
+    x = in_feats.reshape(-1, k)
+    out = torch.empty((m, n // 2), dtype=torch.float16, device=x.device)
+    with _on(x.device):
+        check(lib.kairos_w4a16_decode_silu(_chk(x, torch.float16, 'in_feats'), _chk(kernel, torch.int16, 'kernel'),
+                                           _chk(scaling_factors, torch.float16, 'scaling_factors'),
+                                           _chk(zeros, torch.float16, 'zeros'), _bias_ptr(bias), out.data_ptr(), m, n, k,
+                                           stream_ptr()), 'decode_silu_forward')
+    return out
+
+
 def gemm_forward_cuda_new(in_feats, kernel, scaling_factors, zeros, bias=None):
     k = in_feats.shape[-1]
     x = in_feats.reshape(-1, k)
@@ -203,14 +216,15 @@ def rms_norm(x, weight, eps, residual_delta=None):
     return y
 
 
-def silu_mul(gate_up):
-    """silu(gate) * up for the fused activation [..., 2I] -> [..., I]."""
+def silu_mul(gate_up, blocked=False):
+    """silu(gate) * up for the fused activation [..., 2I] -> [..., I]; `blocked`: gate and up channels alternate
+    in blocks of 16 (see the header) instead of lying one after the other."""
     i2 = gate_up.shape[-1]
     m = gate_up.numel() // i2
     out = torch.empty(gate_up.shape[:-1] + (i2 // 2,), dtype=torch.float16, device=gate_up.device)
+    fn = lib.kairos_silu_mul_blocked if blocked else lib.kairos_silu_mul
     with _on(gate_up.device):
-        check(lib.kairos_silu_mul(_chk(gate_up, torch.float16, 'gate_up'), out.data_ptr(), m, i2 // 2, stream_ptr()),
-              'silu_mul')
+        check(fn(_chk(gate_up, torch.float16, 'gate_up'), out.data_ptr(), m, i2 // 2, stream_ptr()), 'silu_mul')
     return out
 
 
@@ -250,7 +264,7 @@ def rms_norm_quant(x, weight, eps, want_f16=False, residual_delta=None):
     return xq, sx, y
 
 
-def silu_mul_quant(gate_up, want_f16=False):
+def silu_mul_quant(gate_up, want_f16=False, blocked=False):
     """silu(gate) * up emitting per-token int8 + fp16 scales.  Returns (xq, sx, y_or_None)."""
     i2 = gate_up.shape[-1]
     m = gate_up.numel() // i2
@@ -258,7 +272,8 @@ def silu_mul_quant(gate_up, want_f16=False):
     xq = torch.empty(shape, dtype=torch.int8, device=gate_up.device)
     sx = torch.empty((m,), dtype=torch.float16, device=gate_up.device)
     y = torch.empty(shape, dtype=torch.float16, device=gate_up.device) if want_f16 else None
+    fn = lib.kairos_silu_mul_quant_blocked if blocked else lib.kairos_silu_mul_quant
     with _on(gate_up.device):
-        check(lib.kairos_silu_mul_quant(_chk(gate_up, torch.float16, 'gate_up'), None if y is None else y.data_ptr(),
-                                        xq.data_ptr(), sx.data_ptr(), m, i2 // 2, stream_ptr()), 'silu_mul_quant')
+        check(fn(_chk(gate_up, torch.float16, 'gate_up'), None if y is None else y.data_ptr(), xq.data_ptr(),
+                 sx.data_ptr(), m, i2 // 2, stream_ptr()), 'silu_mul_quant')
     return xq, sx, y
