@@ -265,6 +265,15 @@ def measure_int8_peak(torch, device):
         return {'int8_tops_measured': None, 'int8_source': f'unavailable ({type(exc).__name__})'}
 
 
+def rank0_decides(dist, flag, more):
+    """Every rank must run the same number of timed blocks, because a block holds collectives: a rank that went on
+    for one more block on its own clock would wait for its peers forever.  Rank 0's verdict is broadcast; `flag` is
+    a one-element tensor on the backend's device."""
+    flag.fill_(1.0 if more else 0.0)
+    dist.broadcast(flag, src=0)
+    return bool(flag.item())
+
+
 def timed_blocks(torch, dist, world, device, fn, steps, warmup, min_seconds=1.0, max_blocks=400, mark=False):
     """Device time of `steps` calls of fn, repeated as blocks until the timed region is at least `min_seconds`
     long (so that clock samples fall inside it); every block is bracketed by events, barrier + synchronize
@@ -289,10 +298,7 @@ def timed_blocks(torch, dist, world, device, fn, steps, warmup, min_seconds=1.0,
         blocks.append(s.elapsed_time(e) / steps)
         more = len(blocks) < max_blocks and time.perf_counter() - t_start < min_seconds
         if world > 1:
-            # every rank must run the same number of blocks (fn holds collectives): rank 0's clock decides
-            go_on.fill_(1.0 if more else 0.0)
-            dist.broadcast(go_on, src=0)
-            more = bool(go_on.item())
+            more = rank0_decides(dist, go_on, more)
         if not more:
             break
     torch.cuda.synchronize()

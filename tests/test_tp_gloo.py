@@ -146,3 +146,27 @@ def test_rank_that_never_arrives_is_detected_on_the_host():
     assert (kind, missing, step) == ('lost', [1], 2)
     assert 0.9 < waited < 3.0
     assert out['collective'][0] == 'error' and out['collective'][2] < 15.0
+
+
+def _block_count_worker(rank, world, port, out):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    import bench
+    flag = torch.ones(1)
+    # the ranks' own clocks disagree about going on (rank 1 would run one more block): rank 0's verdict holds
+    mine = [(True, True, False), (True, False, True)][rank]          # what each rank's own clock says, block by block
+    verdicts = [bench.rank0_decides(dist, flag, m) for m in mine]
+    out[rank] = verdicts
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_timed_blocks_agree_on_the_block_count():
+    """bench.py's timed region: both ranks follow rank 0's clock, whatever their own says."""
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_block_count_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert out[0] == [True, True, False]
+    assert out[1] == [True, True, False]
