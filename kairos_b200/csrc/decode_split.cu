@@ -120,7 +120,8 @@ struct SplitCfg {
     static constexpr int kOut = kRows * 8 * NT;                // outputs of a row tile
     static constexpr int kRingBytes = kStages * kStageBytes > kOut * 4 ? kStages * kStageBytes : kOut * 4;
     static constexpr int kWarpBytes = kRingBytes + 128;        // + the stage barriers
-    static constexpr int kMinBlocks = NT == 1 ? 5 : (NT == 2 ? 4 : 2);
+    // (five resident CTAs per SM cap the four-row-block variants at 96 registers, which spills; four leave 128)
+    static constexpr int kMinBlocks = NT == 1 ? (RB == 4 ? 4 : 5) : (NT == 2 ? (RB == 4 ? 2 : 4) : 2);
     static size_t smem_bytes(int warps, int cluster) {
         return 128 + (size_t)warps * kWarpBytes + 16 + (cluster > 1 ? (size_t)cluster * kOut * 4 : 0);
     }
